@@ -1,0 +1,182 @@
+// Host side of the tcgen05 GEMMs: tensor maps, launches, and the Newton-Schulz
+// product schedules built from them.
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+
+namespace dionw {
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library itself
+// links against the CUDA runtime only and still loads on a machine without a GPU.
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// 3-D map over a batch of row-major 2-byte matrices: (inner, rows, batch).
+int make_map(CUtensorMap* map, const void* base, int dtype, int64_t inner, int64_t rows, int64_t batches,
+             int64_t ld, int64_t batch_stride, uint32_t box_inner, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return DIONW_ERR_CUDA;
+  }
+  DIONW_REQUIRE(aligned16(base), "matrix base address must be 16-byte aligned");
+  DIONW_REQUIRE(ld % 8 == 0 && batch_stride % 8 == 0,
+                "leading dimension (%lld) and batch stride (%lld) must be multiples of 8 elements",
+                (long long)ld, (long long)batch_stride);
+  cuuint64_t dims[3] = {cuuint64_t(inner), cuuint64_t(rows), cuuint64_t(batches)};
+  cuuint64_t strides[2] = {cuuint64_t(ld) * 2, cuuint64_t(batch_stride) * 2};
+  if (batches == 1) strides[1] = cuuint64_t(ld) * 2 * cuuint64_t(rows);
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  const CUtensorMapDataType type = dtype == DIONW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult res = fn(map, type, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (inner=%lld rows=%lld batches=%lld ld=%lld)", int(res),
+              (long long)inner, (long long)rows, (long long)batches, (long long)ld);
+    return DIONW_ERR_CUDA;
+  }
+  return DIONW_OK;
+}
+
+template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Params& p, cudaStream_t stream) {
+  auto kernel = gemm::gemm_kernel<InT, OutT, kBMajorMN, kSym>;
+  static bool configured = false;
+  if (!configured) {
+    DIONW_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm::kSmemBytes)));
+    configured = true;
+  }
+  const int total = p.tiles_per_batch * p.batches;
+  if (total == 0) return DIONW_OK;
+  const int grid = total < sm_count() ? total : sm_count();
+  kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(map_a, map_b, p);
+  return launch_status("gemm_kernel launch");
+}
+
+int host_sym_tiles(int tiles_m) {
+  const int q = tiles_m / 2;
+  return q * (q + 1) + ((tiles_m & 1) ? q + 1 : 0);
+}
+
+}  // namespace
+
+// C = alpha A A^T + beta Cin (lower tiles + mirror), optional second output with diag added.
+int symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, int64_t lda, int64_t a_batch,
+                      const void* cin, int64_t ldc, int64_t cin_batch, float alpha, float beta, void* out,
+                      int64_t ldo, int64_t out_batch, void* out2, float diag, int dtype, cudaStream_t stream) {
+  DIONW_REQUIRE(dtype == DIONW_F16 || dtype == DIONW_BF16, "symmetric_product: dtype must be F16 or BF16");
+  DIONW_REQUIRE(blocks > 0 && m > 0 && kdim > 0, "symmetric_product: empty problem");
+  CUtensorMap map_a, map_b;
+  int st = make_map(&map_a, a, dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBM);
+  if (st != DIONW_OK) return st;
+  st = make_map(&map_b, a, dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBN);
+  if (st != DIONW_OK) return st;
+  gemm::Params p{};
+  p.cin = cin;
+  p.out = out;
+  p.out2 = out2;
+  p.ldc = ldc;
+  p.ldo = ldo;
+  p.cin_batch = cin_batch;
+  p.out_batch = out_batch;
+  p.alpha = alpha;
+  p.beta = beta;
+  p.diag = diag;
+  p.m = int(m);
+  p.n = int(m);
+  p.kdim = int(kdim);
+  p.batches = int(blocks);
+  p.tiles_m = int((m + gemm::kBM - 1) / gemm::kBM);
+  p.tiles_n = int((m + gemm::kBN - 1) / gemm::kBN);
+  p.tiles_per_batch = host_sym_tiles(p.tiles_m);
+  p.status = device_status_word();
+  if (dtype == DIONW_F16) return launch<__half, __half, false, true>(map_a, map_b, p, stream);
+  return launch<__nv_bfloat16, __nv_bfloat16, false, true>(map_a, map_b, p, stream);
+}
+
+// C = A B + beta Cin.
+int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int64_t ldb, int64_t b_batch,
+                 bool b_is_nk, const void* cin, int64_t ldc, int64_t cin_batch, float beta, void* out, int64_t ldo,
+                 int64_t out_batch, int64_t blocks, int64_t m, int64_t n, int64_t kdim, int in_dtype, int out_dtype,
+                 cudaStream_t stream) {
+  DIONW_REQUIRE(in_dtype == DIONW_F16 || in_dtype == DIONW_BF16, "batched_gemm: input dtype must be F16 or BF16");
+  DIONW_REQUIRE(out_dtype == DIONW_F16 || out_dtype == DIONW_BF16, "batched_gemm: output dtype must be F16 or BF16");
+  DIONW_REQUIRE(blocks > 0 && m > 0 && n > 0 && kdim > 0, "batched_gemm: empty problem");
+  CUtensorMap map_a, map_b;
+  int st = make_map(&map_a, a, in_dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBM);
+  if (st != DIONW_OK) return st;
+  if (b_is_nk) {
+    st = make_map(&map_b, b, in_dtype, kdim, n, blocks, ldb, b_batch, gemm::kBK, gemm::kBN);
+  } else {
+    st = make_map(&map_b, b, in_dtype, n, kdim, blocks, ldb, b_batch, 64, gemm::kBK);
+  }
+  if (st != DIONW_OK) return st;
+  gemm::Params p{};
+  p.cin = cin;
+  p.out = out;
+  p.out2 = nullptr;
+  p.ldc = ldc;
+  p.ldo = ldo;
+  p.cin_batch = cin_batch;
+  p.out_batch = out_batch;
+  p.alpha = 1.0f;
+  p.beta = beta;
+  p.diag = 0.0f;
+  p.m = int(m);
+  p.n = int(n);
+  p.kdim = int(kdim);
+  p.batches = int(blocks);
+  p.tiles_m = int((m + gemm::kBM - 1) / gemm::kBM);
+  p.tiles_n = int((n + gemm::kBN - 1) / gemm::kBN);
+  p.tiles_per_batch = p.tiles_m * p.tiles_n;
+  p.status = device_status_word();
+  const bool f16 = in_dtype == DIONW_F16;
+  const bool out_same = out_dtype == in_dtype;
+  if (b_is_nk) {
+    if (f16 && out_same) return launch<__half, __half, false, false>(map_a, map_b, p, stream);
+    if (f16) return launch<__half, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
+    if (out_same) return launch<__nv_bfloat16, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
+  } else {
+    if (f16 && out_same) return launch<__half, __half, true, false>(map_a, map_b, p, stream);
+    if (f16) return launch<__half, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
+    if (out_same) return launch<__nv_bfloat16, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
+  }
+  set_error("batched_gemm: bf16 inputs with an fp16 output are not supported");
+  return DIONW_ERR_UNSUPPORTED;
+}
+
+}  // namespace dionw
+
+extern "C" int dionw_symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, int64_t lda,
+                                       const void* cin, int64_t ldc, float alpha, float beta, void* out,
+                                       int64_t ldo, void* out2, float diag, int dtype, void* stream) {
+  return dionw::symmetric_product(a, blocks, m, kdim, lda, m * lda, cin, ldc, m * ldc, alpha, beta, out, ldo,
+                                  m * ldo, out2, diag, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int b_is_nk,
+                                  const void* cin, int64_t ldc, float beta, void* out, int64_t ldo, int64_t blocks,
+                                  int64_t m, int64_t n, int64_t kdim, int in_dtype, int out_dtype, void* stream) {
+  const int64_t b_rows = b_is_nk ? n : kdim;
+  return dionw::batched_gemm(a, lda, m * lda, b, ldb, b_rows * ldb, b_is_nk != 0, cin, ldc, m * ldc, beta, out, ldo,
+                             m * ldo, blocks, m, n, kdim, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,214 @@
+/*
+ * dionw_b200 — C ABI of the B200 (sm_100a) optimizer-step kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and the CUDA stream to
+ * launch on (passed as void* so that this header needs no CUDA include), runs
+ * asynchronously on that stream, allocates nothing, never synchronises, and
+ * returns DIONW_OK or a negative code; dionw_last_error() then gives the text.
+ * The reference has no FFI of its own: each entry replaces the Python/Triton
+ * function cited beside it (paths are relative to the reference project).
+ *
+ * Conventions
+ *   - "blocks x rows x cols": the bucket layout of src/dionw/_buckets.py:154-178
+ *     (momentum [blocks, rows, cols] fp32, variance [blocks, rows] fp32).
+ *   - a "run" is a range of consecutive blocks of one bucket whose parameters
+ *     are separate tensors: pointer tables are HOST arrays of DEVICE pointers,
+ *     with rows_per_tensor[i] = rows that tensor i contributes (its blocks x rows).
+ *   - dtype codes: DIONW_F32 / DIONW_F16 / DIONW_BF16.
+ */
+#ifndef DIONW_B200_H_
+#define DIONW_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DIONW_OK 0
+#define DIONW_ERR_ARGUMENT (-1)
+#define DIONW_ERR_CUDA (-2)
+#define DIONW_ERR_WORKSPACE (-3)
+#define DIONW_ERR_UNSUPPORTED (-4)
+#define DIONW_ERR_DEVICE_WAIT (-5)
+#define DIONW_ERR_WORKER (-6)
+
+#define DIONW_F32 0
+#define DIONW_F16 1
+#define DIONW_BF16 2
+
+/* Newton-Schulz kinds (src/dionw/newton_schulz.py:33-40). */
+#define DIONW_NS_GRAM 0
+#define DIONW_NS_POLAR_EXPRESS 1
+#define DIONW_NS_KELLER 2
+
+/* Text of the last error on the calling thread (copied, NUL-terminated). */
+void dionw_last_error(char* buffer, size_t size);
+/* Library version string. */
+const char* dionw_version(void);
+/* Reads and clears the device status word (non-zero: a bounded wait inside a
+ * kernel ran out).  Synchronises the device; meant for tests and diagnostics. */
+int dionw_device_status(int* status);
+
+/* ---- momentum passes ---------------------------------------------------- */
+
+/* M += G for every row of a run, plus per-row sum|M| (scores) and sum M^2.
+ * Replaces accumulate_row_l1 / _accumulate_row_l1_kernel
+ * (src/dionw/_momentum_kernels.py:40-55, :89-103) as called once per parameter
+ * by _accumulate_with_scores (src/dionw/_matrix_step.py:188-199); here one
+ * launch covers the whole run.  Score order: 1024 strided lanes, folded by
+ * halving (lane[i] += lane[i+w], w = 512..1). */
+int dionw_accumulate_row_l1_run(const void* const* grads, int grad_dtype,
+                                const int64_t* rows_per_tensor, int n_tensors,
+                                float* momentum, float* scores, float* sumsq,
+                                int64_t cols, void* stream);
+
+/* m = M + G; M = decay*m; u = m (heavy ball) or G + decay*m (Nesterov); also
+ * per-row sum u^2.  Replaces accumulate_copy_decay
+ * (src/dionw/_momentum_kernels.py:58-77, :106-133; caller
+ * src/dionw/_matrix_step.py:217-237). */
+int dionw_accumulate_copy_decay_run(const void* const* grads, int grad_dtype,
+                                    const int64_t* rows_per_tensor, int n_tensors,
+                                    float* momentum, float* u, float* sumsq,
+                                    int64_t cols, float decay, int nesterov, void* stream);
+
+/* Top-k rows of each block by score.  Writes the selected rows in ascending
+ * order (ties go to the lower row), the inverse map rowmap[b, r] = position of
+ * row r in index[b, :] or -1, and frob[b] = sqrt(sum of sumsq over the selected
+ * rows).  Replaces torch.topk + the Frobenius norm of the gathered rows
+ * (src/dionw/_matrix_step.py:172-176, src/dionw/_gram.py:85-86). */
+int dionw_select_rows(const float* scores, const float* sumsq, int64_t blocks,
+                      int64_t rows, int64_t k, int32_t* index, int32_t* rowmap,
+                      float* frob, void* stream);
+
+/* frob[b] = sqrt(sum_r sumsq[b, r]) for blocks that update every row. */
+int dionw_block_norms(const float* sumsq, int64_t blocks, int64_t rows, float* frob,
+                      void* stream);
+
+/* For each listed row: x = half(src_row / (frob[b] + eps)) and, when
+ * decay_rows != 0, src_row *= decay in place (error feedback).  index may be
+ * NULL (every row, k == rows).  x is [blocks, k, ldx] in x_dtype (F16 or BF16;
+ * BF16 also rounds the input first and scales the norm by norm_scale, the
+ * form of src/dionw/_polar_express.py:88-92).  Replaces gather + mul +
+ * scatter_ + normalise + cast (src/dionw/_matrix_step.py:176-179,
+ * src/dionw/_gram.py:85-87). */
+int dionw_pack_rows(float* src, const int32_t* index, const float* frob,
+                    int64_t blocks, int64_t rows, int64_t k, int64_t cols,
+                    float decay, int decay_rows, float eps, float norm_scale,
+                    void* x, int x_dtype, int64_t ldx, void* stream);
+
+/* out[b, c, r] = in[b, r, c] for 2-byte elements (tall blocks are iterated in
+ * their wide orientation, src/dionw/_gram.py:83-84, :89). */
+int dionw_transpose_2byte(const void* in, void* out, int64_t blocks, int64_t rows,
+                          int64_t cols, int64_t ld_in, int64_t ld_out, void* stream);
+
+/* ---- Newton-Schulz ------------------------------------------------------ */
+
+/* Bytes of scratch dionw_newton_schulz needs for this problem. */
+size_t dionw_newton_schulz_workspace_bytes(int64_t blocks, int64_t m, int64_t n, int kind);
+
+/* Five quintic steps on wide or square [blocks, m, ldx] operands (m <= n),
+ * already normalised and rounded to fp16 (GRAM) or bf16 (the other kinds);
+ * x is overwritten; out receives bf16 [blocks, m, ldx].  out may alias x.
+ * GRAM follows gram_polar_express / _gram / _standard (src/dionw/_gram.py:41-89)
+ * product by product, with the symmetric products (ns_line_1, ns_line_2,
+ * src/dionw/_symmetric_kernels.py:252-312) computed on one triangle of tiles
+ * by tcgen05 tensor-core kernels fed by TMA.  POLAR_EXPRESS / KELLER follow
+ * quintic_triton (src/dionw/_polar_express.py:74-104, src/dionw/_keller.py). */
+int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m, int64_t n,
+                        int64_t ldx, int kind, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
+/* C = alpha * A A^T + beta * Cin on the lower triangle of tiles, mirrored;
+ * out2 (optional) = C + diag * I.  A is [blocks, m, lda] with kdim columns.
+ * dtype F16 or BF16 for every operand.  ns_line_1 is alpha=1, beta=0, cin=NULL;
+ * ns_line_2 is A = Cin = the symmetric input
+ * (src/dionw/_symmetric_kernels.py:252-312). */
+int dionw_symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim,
+                            int64_t lda, const void* cin, int64_t ldc, float alpha,
+                            float beta, void* out, int64_t ldo, void* out2, float diag,
+                            int dtype, void* stream);
+
+/* C = A B + beta * Cin, A [blocks, m, lda] (m x kdim).  b_is_nk = 0: B is
+ * [blocks, kdim, ldb] row-major (kdim x n); b_is_nk = 1: B is given as
+ * [blocks, n, ldb] (n x kdim) and used transposed.  cin may be NULL (beta
+ * ignored).  in_dtype F16/BF16; out_dtype F16/BF16 (torch.bmm / torch.baddbmm
+ * at src/dionw/_gram.py:46,58,64,67-69). */
+int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int b_is_nk,
+                       const void* cin, int64_t ldc, float beta, void* out, int64_t ldo,
+                       int64_t blocks, int64_t m, int64_t n, int64_t kdim, int in_dtype,
+                       int out_dtype, void* stream);
+
+/* ---- NorMuon and the weight update -------------------------------------- */
+
+/* s[b*k + r] = sum_c o[b, r, c]^2 for a bf16 batch [blocks, k, ldo]. */
+int dionw_row_sumsq_bf16(const void* o, int64_t blocks, int64_t k, int64_t cols,
+                         int64_t ldo, float* s, void* stream);
+
+/* Per-row and per-block scales of NorMuon (normalize_rows,
+ * src/dionw/_row_normalization.py:41-60): v <- lerp(v, s/cols, weight) written
+ * back to variance[b, index[b, r]] (index NULL: row r); denom = sqrt(v) + eps;
+ * scale[b] = ||O|| / max(||O/denom||, eps) * step.  normalize = 0 gives
+ * denom = 1, scale = step and leaves variance alone
+ * (RowNormalization.NONE, src/dionw/_row_normalization.py:35-36). */
+int dionw_normuon_rows(const float* s, float* variance, const int32_t* index,
+                       int64_t blocks, int64_t rows, int64_t k, int64_t cols,
+                       float weight, float eps, float step, int normalize,
+                       float* denom, float* scale, void* stream);
+
+/* W <- W * decay_factor on every row (when has_decay), then
+ * W[row] += (float(o[b, p, :]) / denom[b, p]) * scale[b] for each selected row
+ * (p = rowmap[b, row] >= 0; rowmap NULL: every row, p = row).  Replaces _apply
+ * / _add_blocks_ (src/dionw/_matrix_step.py:274-304). */
+int dionw_apply_run(void* const* weights, const int64_t* rows_per_tensor, int n_tensors,
+                    const void* o, int64_t ldo, const int32_t* rowmap, const float* denom,
+                    const float* scale, int64_t rows, int64_t k, int64_t cols,
+                    float decay_factor, int has_decay, void* stream);
+
+/* ---- AdamW and EMA ------------------------------------------------------ */
+
+/* Adds one to every fp32 step counter, then one fused decoupled-decay AdamW
+ * update per tensor (bias-corrected, amsgrad off).  Replaces adamw_step
+ * (src/dionw/_adamw.py:25-61: torch._foreach_add_ + torch._fused_adamw_). */
+int dionw_adamw_multi(void* const* params, const void* const* grads, void* const* exp_avg,
+                      void* const* exp_avg_sq, void* const* steps, const int64_t* numels,
+                      int n_tensors, float lr, float beta1, float beta2, float weight_decay,
+                      float eps, void* stream);
+
+/* shadow <- source (first = 1) or shadow += weight * (source - shadow) for
+ * every tensor (weight = 1 - decay < 0.5 form of torch.lerp; else
+ * source - (source - shadow) * (1 - weight)).  source_dtype F32/F16/BF16.
+ * Replaces _finalize_gpu_updates / foreach_ema_update_
+ * (src/dionw/ema/tracker.py:139-152, src/dionw/ema/_update.py:32-70). */
+int dionw_ema_multi(void* const* shadows, const void* const* sources, const int64_t* numels,
+                    int n_tensors, int source_dtype, float weight, int first, void* stream);
+
+/* Gathers n tensors into one contiguous fp32 staging buffer on the device
+ * (element offsets[i]); the caller then issues ONE device-to-host copy.
+ * Replaces the per-parameter copies of _stage_cpu_snapshot
+ * (src/dionw/ema/tracker.py:229-248). */
+int dionw_ema_stage_pack(const void* const* sources, const int64_t* numels,
+                         const int64_t* offsets, int n_tensors, int source_dtype,
+                         float* staging, void* stream);
+
+/* Host worker of the CPU EMA (AsyncCpuEmaJob, src/dionw/ema/_cpu_job.py:46-137):
+ * start() spawns a thread that waits for `cuda_event` (a cudaEvent_t, may be
+ * NULL), then for each of n segments copies (first[i] != 0) or lerps
+ * shadow_i <- shadow_i + weight * (staged_i - shadow_i) on `threads` host threads.
+ * wait_copy() returns once the event has completed, wait_update() once the
+ * shadows are written; done() polls; destroy() joins and frees.  At most the
+ * caller's one job at a time is expected, as in the reference. */
+typedef struct dionw_cpu_ema_job dionw_cpu_ema_job;
+dionw_cpu_ema_job* dionw_cpu_ema_job_start(float* const* shadows, const float* const* staged,
+                                           const int64_t* numels, const uint8_t* first,
+                                           int n, float weight, void* cuda_event, int threads);
+int dionw_cpu_ema_job_wait_copy(dionw_cpu_ema_job* job);
+int dionw_cpu_ema_job_wait_update(dionw_cpu_ema_job* job);
+int dionw_cpu_ema_job_done(dionw_cpu_ema_job* job);
+void dionw_cpu_ema_job_destroy(dionw_cpu_ema_job* job);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIONW_B200_H_ */
