@@ -1,0 +1,424 @@
+"""Optimizer-step benchmark: ``python bench.py --gpus N --steps K --warmup W``.
+
+Workload (N = 1 and up): the Llama-3-8B-shaped parameter set — 32 layers of
+q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336 (Dion3,
+fraction 0.25), 65 RMSNorm[4096] and embed + lm_head 128256x4096 (AdamW); fp32
+masters, synthetic weights ~N(0, 0.02^2) and gradients ~N(0, 1e-3^2), lr 3e-4,
+weight decay 0.05.  A "step" is one ``optimizer.step()`` over the whole set; the
+gradients stay the same tensors across timed steps, as in the reference's own
+benchmark (bench/optimizer_step.py:91-96 there).  Working set (~100 GB) is far
+larger than L2, so nothing is flushed between steps.
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU oracle
+(``oracle/dion_oracle.py``, the restatement of the reference's step pinned by
+its fixtures) on the host cores instead, on a bounded sample of the same
+workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import contextlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+from torch import nn
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LR, WEIGHT_DECAY = 3e-4, 0.05
+CONFIGS = {
+    # name: (layers, d_model, d_kv, d_ff, vocab)
+    "llama3-8b": (32, 4096, 1024, 14336, 128256),
+    "llama3-8b-2layers": (2, 4096, 1024, 14336, 16032),
+    "tiny": (2, 1024, 256, 3584, 4096),
+}
+
+
+# ---------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------
+class Layer(nn.Module):
+    def __init__(self, d: int, dkv: int, dff: int, device) -> None:
+        super().__init__()
+        mk = lambda r, c: nn.Parameter(torch.empty(r, c, device=device))  # noqa: E731
+        self.q, self.k, self.v, self.o = mk(d, d), mk(dkv, d), mk(dkv, d), mk(d, d)
+        self.gate, self.up, self.down = mk(dff, d), mk(dff, d), mk(d, dff)
+        self.norm1 = nn.Parameter(torch.empty(d, device=device))
+        self.norm2 = nn.Parameter(torch.empty(d, device=device))
+
+
+class LlamaShaped(nn.Module):
+    """Only the parameters: nothing here is ever run forward."""
+
+    def __init__(self, name: str, device) -> None:
+        super().__init__()
+        layers, d, dkv, dff, vocab = CONFIGS[name]
+        self.embed = nn.Embedding(vocab, d, device=device)
+        self.layers = nn.ModuleList(Layer(d, dkv, dff, device) for _ in range(layers))
+        self.norm = nn.Parameter(torch.empty(d, device=device))
+        self.lm_head = nn.Linear(d, vocab, bias=False, device=device)
+
+    @torch.no_grad()
+    def init_(self, seed: int) -> None:
+        gen = torch.Generator(device=self.norm.device).manual_seed(seed)
+        for p in self.parameters():
+            p.normal_(0.0, 0.02, generator=gen)
+
+
+def flops_newton_schulz(m: int, n: int) -> float:
+    """Algorithmic FLOPs of one orthogonalization of an m x n operand (m <= n): the Gram
+    schedule's product census, symmetric products counted as half."""
+    if m == n:
+        return 2.0 * 10.0 * m**3
+    return 2.0 * (3.0 * m * m * n + 11.5 * m**3)
+
+
+def census(model: LlamaShaped, fraction: float = 0.25, min_dim: int = 1024) -> dict[str, float]:
+    """Algorithmic work of one step: elements, bytes per pass, Newton-Schulz FLOPs."""
+    e = es = ns = adam = 0.0
+    for layer in model.layers:
+        for w in (layer.q, layer.k, layer.v, layer.o, layer.gate, layer.up, layer.down):
+            rows, cols = w.shape
+            k = -(-int(fraction * rows * 1e9) // int(1e9)) if min(rows, cols) >= min_dim else rows
+            k = min(rows, max(k, 1))
+            e += rows * cols
+            es += k * cols
+            ns += flops_newton_schulz(min(k, cols), max(k, cols))
+    for p in model.parameters():
+        adam += p.numel()
+    adam -= e
+    return {
+        "matrix_elements": e, "selected_elements": es, "adamw_elements": adam, "ns_flops": ns,
+        "bytes_accumulate": 12 * e, "bytes_pack": 10 * es, "bytes_finish": 2 * es,
+        "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam,
+    }
+
+
+# ---------------------------------------------------------------------------
+# timing helpers
+# ---------------------------------------------------------------------------
+class StageTimer:
+    """Brackets the stages of every run (and the AdamW groups) with CUDA events on the
+    current stream; ``collect()`` sums milliseconds per stage after a synchronize."""
+
+    def __init__(self) -> None:
+        self.events: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+        self.enabled = False
+
+    @contextlib.contextmanager
+    def __call__(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        yield
+        end.record()
+        self.events.append((name, start, end))
+
+    def collect(self) -> dict[str, float]:
+        torch.cuda.synchronize()
+        totals: dict[str, float] = {}
+        for name, start, end in self.events:
+            totals[name] = totals.get(name, 0.0) + start.elapsed_time(end)
+        self.events.clear()
+        return totals
+
+
+class ClockSampler:
+    """``nvidia-smi`` sampling of SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.file = index, None, None
+
+    def start(self) -> None:
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict | None:
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 6]
+        os.unlink(self.file.name)
+        if not rows:
+            return None
+        sm = [float(r[0]) for r in rows if r[0].strip().replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any("Active" == r[3 + i].strip() for r in rows)]
+        loaded = [v for v in sm if v > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": float(rows[0][1]), "samples": len(rows),
+                "power_w_max": max(float(r[2]) for r in rows), "reasons": reasons}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# the CPU arm (oracle) — also the cpu_baseline of the GPU arm
+# ---------------------------------------------------------------------------
+def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
+    """Times the CPU oracle on one layer's attention blocks (q, o: d x d; k, v: dkv x d) and
+    one RMSNorm vector, then scales the matrix time by Newton-Schulz FLOPs and the AdamW time
+    by elements to the whole parameter set."""
+    from oracle import dion_oracle as oracle
+
+    layers, d, dkv, dff, vocab = CONFIGS[config]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(0)
+    shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
+    weights = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
+    norm = torch.randn(d, generator=gen) * 0.02
+    grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
+    gnorm = torch.randn(d, generator=gen) * 1e-3
+    opt = oracle.OracleDion(matrix=[(w, 0.25 if min(w.shape) >= 1024 else 1.0) for w in weights],
+                            adamw=[(norm, 0.0)], lr=LR, weight_decay=WEIGHT_DECAY)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        opt.step(grads, [gnorm])
+        if i >= warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+    sample_flops = sum(flops_newton_schulz(*sorted((min(r, -(-r // 4) if min(r, c) >= 1024 else r), c)))
+                       for r, c in shapes)
+    model_flops = 0.0
+    for r, c in [(d, d)] * 2 + [(dkv, d)] * 2 + [(dff, d)] * 2 + [(d, dff)]:
+        k = -(-r // 4) if min(r, c) >= 1024 else r
+        model_flops += layers * flops_newton_schulz(min(k, c), max(k, c))
+    per_step = statistics.median(times)
+    scaled = per_step * model_flops / sample_flops
+    return {
+        "value": scaled, "unit": "ms", "cores": cores, "kind": "port",
+        "sample": (f"CPU oracle (torch eager, {cores} threads) on one layer's q, o ({d}x{d}) and k, v ({dkv}x{d}) "
+                   f"blocks + one RMSNorm[{d}]: median {per_step:.1f} ms per sample step over {steps} steps, "
+                   f"scaled by Newton-Schulz FLOPs x{model_flops / sample_flops:.0f} to the whole set"),
+        "sample_ms": per_step,
+    }
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_sample_step(args.config, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "optimizer_step_ms", "value": base["value"], "unit": "ms",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["value"],
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp32 state, fp16 Newton-Schulz", "data": "synthetic",
+        "config": {"workload": args.config, "arm": "reference's algorithm on host CPU cores (oracle port)"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# the GPU arm
+# ---------------------------------------------------------------------------
+def run_gpu_arm(args) -> None:
+    import dionw_b200 as dionw
+    from dionw_b200 import _adamw, _matrix_step, _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    _native.library()
+
+    model = LlamaShaped(args.config, device)
+    model.init_(seed=0)
+    routes = {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
+    groups, _ = dionw.param_groups(model, routes=routes)
+    if distributed:
+        from dionw_b200.distributed import ShardedDion
+
+        optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+    else:
+        optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+    gen = torch.Generator(device=device).manual_seed(1)
+    for p in model.parameters():
+        p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
+    work = census(model)
+
+    def barrier() -> None:
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    timer = StageTimer()
+    _matrix_step.STAGE_HOOK = timer
+    real_adamw = _adamw.adamw_step
+
+    def timed_adamw(group, state):
+        with timer("adamw"):
+            real_adamw(group, state)
+
+    import dionw_b200.optimizer as optimizer_module
+    optimizer_module.adamw_step = timed_adamw
+
+    for _ in range(args.warmup):
+        optimizer.step()
+    barrier()
+
+    # ---- timed region: exactly K steps, device time, max over ranks
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches_before = _native.launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        optimizer.step()
+    end.record()
+    barrier()
+    total_ms = start.elapsed_time(end)
+    launches = _native.launch_count() - launches_before
+    clocks = sampler.stop()
+    if distributed:
+        t = torch.tensor([total_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t)
+    ms_per_step = total_ms / args.steps
+
+    # ---- per-stage device time (separate steps so the events do not sit in the timed region)
+    timer.enabled = True
+    stage_steps = max(1, min(3, args.steps))
+    for _ in range(stage_steps):
+        optimizer.step()
+    stages = {k: v / stage_steps for k, v in timer.collect().items()}
+    timer.enabled = False
+
+    # ---- end to end: gradients come from pinned host memory, one scalar goes back
+    pool: dict[tuple, torch.Tensor] = {}
+    for p in model.parameters():
+        key = tuple(p.shape)
+        if key not in pool:
+            pool[key] = torch.empty(p.shape, dtype=torch.float32, pin_memory=True).normal_(0.0, 1e-3)
+    result_host = torch.empty((), dtype=torch.float32, pin_memory=True)
+    h2d_bytes = sum(p.numel() * 4 for p in model.parameters())
+    e2e_steps = max(1, min(3, args.steps))
+
+    def e2e_step() -> None:
+        for p in model.parameters():
+            p.grad.copy_(pool[tuple(p.shape)], non_blocking=True)
+        optimizer.step()
+        result_host.copy_(model.norm.sum(), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2) / e2e_steps
+    if distributed:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t)
+
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    peaks, peaks_kind = measured_peaks()
+    share = 1.0 / world  # matrix blocks and the AdamW space are sharded evenly by cost
+    ns_ms = stages.get("newton_schulz", 0.0)
+    ns_tflops = work["ns_flops"] * share / ns_ms / 1e9 if ns_ms else None
+    peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+
+    def gbs(key: str, stage: str, scale: float = 1.0) -> float | None:
+        ms = stages.get(stage, 0.0)
+        return work[key] * scale / ms / 1e6 if ms else None
+
+    stage_report = {
+        "accumulate": {"ms": stages.get("accumulate"), "GB/s": gbs("bytes_accumulate", "accumulate", share)},
+        "select": {"ms": stages.get("select")},
+        "pack": {"ms": stages.get("pack"), "GB/s": gbs("bytes_pack", "pack", share)},
+        "newton_schulz": {"ms": ns_ms, "TFLOP/s": ns_tflops},
+        "finish": {"ms": stages.get("finish"), "GB/s": gbs("bytes_finish", "finish", share)},
+        "apply": {"ms": stages.get("apply"), "GB/s": gbs("bytes_apply", "apply")},
+        "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
+        "hbm_peak_GB/s": peaks["hbm_gbs"],
+    }
+    cpu = cpu_sample_step(args.config, 5, 1) if world == 1 and not args.no_cpu_baseline else None
+    line = {
+        "metric": "optimizer_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp32 state, fp16 Newton-Schulz (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
+                   "lr": LR, "weight_decay": WEIGHT_DECAY, "l2": "working set >> L2 (126 MB), no flush needed",
+                   "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)"},
+        "roofline": {
+            "kernel": "gemm_kernel (all Newton-Schulz products of a step)",
+            "bound": "tensor", "achieved": ns_tflops, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": ns_tflops / peak_tf if ns_tflops else None, "traffic": None,
+            "peak_kind": f"{peaks_kind} bf16 cuBLAS, sustained (the kernel is timed inside the step)",
+            "flops_per_step": work["ns_flops"] * share,
+        },
+        "stages": stage_report,
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
+                "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    parser.add_argument("--config", choices=sorted(CONFIGS), default="llama3-8b")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,183 @@
+"""One Dion step for a run of consecutive bucket parameters that have gradients.
+
+Stages (the arithmetic is that of src/dionw/_matrix_step.py:104-311):
+
+1. accumulate: ``M += G`` and, for row-selecting blocks, every row's l1 score
+   and sum of squares -- one launch for the whole run;
+2. select: the top-k rows of each block; those rows of ``M`` are decayed (error
+   feedback) while being packed, normalised, into the fp16 operand;
+   blocks that update every row decay all of ``M`` instead;
+3. orthogonalize: the group's Newton-Schulz on the tensor cores;
+4. finish: NorMuon row statistics (or none) reduced to one scale per row and
+   one per block;
+5. apply: decoupled weight decay on every row and the scaled update on the
+   selected rows, in one pass over the weights.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Callable, Sequence
+from contextlib import AbstractContextManager, nullcontext
+from typing import Any
+
+import torch
+from torch import Tensor
+
+from dionw_b200 import _native, _workspace
+from dionw_b200._buckets import Bucket
+from dionw_b200._keys import MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, ROW_NORMALIZATION_KEY, ParamState
+from dionw_b200.matrix_update import MomentumForm, RowNormalization
+from dionw_b200.newton_schulz import NativeOrthogonalizer, padded, run_iteration
+
+__all__ = ["MAX_RUN_ELEMENTS", "run_elements", "step_run"]
+
+ADAMW_UPDATE_RMS = 0.2        # update RMS of AdamW that matrix steps are matched to
+NEWTON_SCHULZ_EPS = 1e-8      # added to the Frobenius norm; independent of AdamW's eps
+NORMALIZATION_EPS = 1e-8      # NorMuon's epsilon
+# Most update elements (blocks x selected rows x cols) one run orthogonalizes at
+# once; bounds the transient memory of a step (src/dionw/_matrix_step.py:44-50).
+MAX_RUN_ELEMENTS = 2**28
+
+
+# Optional observer: ``STAGE_HOOK(name)`` must return a context manager; it is
+# entered around each stage of a run ("accumulate", "select", "pack",
+# "newton_schulz", "finish", "apply").  The benchmark uses it to bracket stages
+# with CUDA events; None costs nothing.
+STAGE_HOOK: Callable[[str], AbstractContextManager[object]] | None = None
+
+
+def _stage(name: str) -> AbstractContextManager[object]:
+    return nullcontext() if STAGE_HOOK is None else STAGE_HOOK(name)
+
+
+def run_elements(bucket: Bucket, position: int) -> int:
+    """Update elements of the parameter at ``position`` of ``bucket``."""
+    blocks = bucket.slices[position]
+    return (blocks.stop - blocks.start) * bucket.selected_rows * bucket.cols
+
+
+def step_size(bucket: Bucket, lr: float) -> float:
+    """``lr * 0.2 * sqrt(max(rows, cols)) * sqrt(min(rows, cols) / min(k, cols))``."""
+    rows, cols, k = bucket.rows, bucket.cols, bucket.selected_rows
+    return lr * ADAMW_UPDATE_RMS * math.sqrt(max(rows, cols)) * math.sqrt(min(rows, cols) / min(k, cols))
+
+
+def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], state: ParamState) -> None:
+    """Apply one Dion step to bucket parameters ``positions`` (consecutive, all with gradients).
+
+    Raises:
+        RuntimeError: If a parameter has no gradient.
+    """
+    del state  # momentum and variance are reached through the bucket's own buffers
+    params = [bucket.params[i] for i in positions]
+    grads: list[Tensor] = []
+    for param in params:
+        if param.grad is None:
+            raise RuntimeError("a Dion run holds a parameter without a gradient")
+        grads.append(param.grad)
+    # The kernels walk row-major memory: a channels-last gradient or weight is
+    # packed first (and the weight written back afterwards).
+    if len({g.dtype for g in grads}) > 1:
+        grads = [g.float() for g in grads]
+    grads = [g if g.is_contiguous() else g.contiguous() for g in grads]
+    targets = [p if p.is_contiguous() else p.detach().contiguous() for p in params]
+
+    blocks = bucket.run_blocks(positions)
+    count = blocks.stop - blocks.start
+    rows, cols, k = bucket.rows, bucket.cols, bucket.selected_rows
+    momentum = bucket.momentum[blocks]
+    variance = bucket.variance[blocks].view(count, rows)
+    rows_per_tensor = [(bucket.slices[i].stop - bucket.slices[i].start) * rows for i in positions]
+    lr = float(group["lr"])
+    step = -step_size(bucket, lr)
+    bucket.step_scale = step
+    decay = float(group[MOMENTUM_KEY])
+    selecting = k < rows
+    fn = bucket.orthogonalize
+    native = isinstance(fn, NativeOrthogonalizer)
+    dtype = fn.dtype if native else torch.float16
+    device = momentum.device
+
+    plan: dict[str, tuple[tuple[int, ...], torch.dtype]] = {
+        "scores": ((count, rows), torch.float32),
+        "sumsq": ((count, rows), torch.float32),
+        "index": ((count, k), torch.int32),
+        "rowmap": ((count, rows), torch.int32),
+        "frob": ((count,), torch.float32),
+        "rowsq": ((count * k,), torch.float32),
+        "denom": ((count * k,), torch.float32),
+        "scale": ((count,), torch.float32),
+        "x": ((count, k, padded(cols)), dtype),
+    }
+    if not selecting:
+        plan["u"] = ((count, rows, cols), torch.float32)
+    if native:
+        plan["ns"] = ((fn.workspace_bytes(count, k, cols),), torch.uint8)
+        if k > cols:
+            plan["xt"] = ((count, cols, padded(k)), dtype)
+    buf = _workspace.carve(device, plan)
+
+    # 1-2: accumulate, select, decay, pack
+    if selecting:
+        with _stage("accumulate"):
+            _native.accumulate_row_l1_run(grads, rows_per_tensor, momentum, buf["scores"], buf["sumsq"], cols)
+        with _stage("select"):
+            _native.select_rows(buf["scores"], buf["sumsq"], k, buf["index"], buf["rowmap"], buf["frob"])
+        index, rowmap, source = buf["index"], buf["rowmap"], momentum
+    else:
+        nesterov = MomentumForm(group[MOMENTUM_FORM_KEY]) is MomentumForm.NESTEROV
+        with _stage("accumulate"):
+            _native.accumulate_copy_decay_run(grads, rows_per_tensor, momentum, buf["u"], buf["sumsq"], cols, decay,
+                                              nesterov)
+            _native.block_norms(buf["sumsq"], buf["frob"])
+        index, rowmap, source = None, None, buf["u"]
+
+    # 3: orthogonalize
+    if native:
+        with _stage("pack"):
+            _native.pack_rows(source, index, buf["frob"], k, buf["x"], decay=decay, decay_rows=selecting,
+                              eps=NEWTON_SCHULZ_EPS, norm_scale=fn.norm_scale)
+        with _stage("newton_schulz"):
+            orthogonal = run_iteration(fn, buf["x"], k, cols, buf["ns"], buf.get("xt"))
+    else:
+        orthogonal = _foreign_orthogonalize(fn, source, index, decay, selecting, buf["x"])
+
+    # 4: row and block scales
+    normalize = RowNormalization(group[ROW_NORMALIZATION_KEY]) is RowNormalization.NORMUON
+    with _stage("finish"):
+        if normalize:
+            _native.row_sumsq_bf16(orthogonal, cols, buf["rowsq"])
+        _native.normuon_rows(buf["rowsq"], variance, index, blocks=count, rows=rows, k=k, cols=cols,
+                             weight=1.0 - float(group[MUON_BETA2_KEY]), eps=NORMALIZATION_EPS, step=step,
+                             normalize=normalize, denom=buf["denom"], scale=buf["scale"])
+
+    # 5: decay + update
+    weight_decay = float(group["weight_decay"])
+    with _stage("apply"):
+        _native.apply_run(targets, rows_per_tensor, orthogonal, rowmap, buf["denom"], buf["scale"], rows=rows, k=k,
+                          cols=cols, decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0)
+    for param, target in zip(params, targets):
+        if target is not param:
+            param.copy_(target)
+
+
+def _foreign_orthogonalize(fn: Any, source: Tensor, index: Tensor | None, decay: float, selecting: bool,
+                           out: Tensor) -> Tensor:
+    """Orthogonalize with a caller-supplied function (``[N, k, cols]`` fp32 -> bf16).
+
+    The built-in kinds never come here.  A test or a user that swaps
+    ``_buckets.newton_schulz_fn`` for its own function gets the rows gathered
+    in fp32 with torch indexing, its function called, and the bf16 result
+    copied into the padded operand buffer the later kernels read.
+    """
+    if selecting:
+        wide = index.long().unsqueeze(-1).expand(-1, -1, source.shape[-1])
+        matrices = torch.gather(source, 1, wide)
+        source.scatter_(1, wide, matrices * decay)
+    else:
+        matrices = source
+    result = fn(matrices, NEWTON_SCHULZ_EPS)
+    target = out.view(torch.bfloat16) if out.dtype is not torch.bfloat16 else out
+    target[..., : matrices.shape[-1]].copy_(result)
+    return target

@@ -39,6 +39,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_last_error": (None, (ctypes.c_char_p, c_size_t)),
     "dionw_version": (c_char_p, ()),
     "dionw_device_status": (c_int, (POINTER(c_int),)),
+    "dionw_launch_count": (c_int64, ()),
     "dionw_accumulate_row_l1_run": (c_int, (_PP, c_int, _I64P, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p)),
     "dionw_accumulate_copy_decay_run": (
         c_int, (_PP, c_int, _I64P, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p)),
@@ -132,6 +133,11 @@ def dtype_code(dtype: torch.dtype) -> int:
         return _DTYPE_CODE[dtype]
     except KeyError:
         raise TypeError(f"dionw_b200 kernels take float32, float16 or bfloat16, got {dtype}") from None
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(library().dionw_launch_count())
 
 
 def device_status() -> int:
@@ -267,7 +273,7 @@ def ema_stage_pack(sources: Sequence[Tensor], offsets: Sequence[int], staging: T
         return
     _check(library().dionw_ema_stage_pack(
         _ptr_array(sources), _i64_array([s.numel() for s in sources]), _i64_array(offsets), len(sources),
-        dtype_code(sources[0].dtype), staging.data_ptr(), _stream(staging)))
+        dtype_code(sources[0].dtype), staging.data_ptr(), _stream(sources[0])))
 
 
 class CpuEmaJob:

@@ -13,6 +13,7 @@
 namespace dionw {
 namespace {
 thread_local char g_error[512] = "";
+std::atomic<long long> g_launches{0};
 __device__ int g_device_status = 0;
 }  // namespace
 
@@ -22,6 +23,8 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_error, sizeof(g_error), fmt, args);
   va_end(args);
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int* device_status_word() {
   static thread_local int* cached[64] = {nullptr};
@@ -43,6 +46,8 @@ extern "C" void dionw_last_error(char* buffer, size_t size) {
 }
 
 extern "C" const char* dionw_version(void) { return "dionw_b200 0.1.0 (sm_100a)"; }
+
+extern "C" int64_t dionw_launch_count(void) { return dionw::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int dionw_device_status(int* status) {
   using namespace dionw;

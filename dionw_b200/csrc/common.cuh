@@ -40,7 +40,13 @@ inline int check_cuda(cudaError_t err, const char* what) {
     }                                                      \
   } while (0)
 
-inline int launch_status(const char* what) { return check_cuda(cudaGetLastError(), what); }
+// Adds one to the library's count of kernel launches (dionw_launch_count()).
+void count_launch();
+
+inline int launch_status(const char* what) {
+  count_launch();
+  return check_cuda(cudaGetLastError(), what);
+}
 
 inline int sm_count() {
   static int cached[64] = {0};

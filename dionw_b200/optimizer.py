@@ -1,0 +1,269 @@
+"""``Dion``: row-selected NorMuon on matrices, AdamW on the rest, one learning rate.
+
+The API, validation, messages, ``state_dict`` layout and resume checks are those
+of the reference's ``dionw.Dion`` (src/dionw/optimizer.py:81-424); the step runs
+on this package's sm_100a kernels through the C ABI of ``include/dionw_b200.h``.
+
+Per matrix block and step: ``M += G``; keep the top ``k = ceil(fraction * rows)``
+rows of ``M`` by l1 norm and decay them by ``momentum`` (error feedback); run
+five Newton-Schulz steps on the kept rows; NorMuon divides each row by the root
+of an EMA of its mean square and restores the block's Frobenius norm;
+``W[rows] -= lr * 0.2 * sqrt(max(rows, cols)) * sqrt(min(rows, cols) / min(k, cols)) * O``;
+weight decay is decoupled and touches every row.  Parameters must be float32 on
+a CUDA device.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable, Iterable
+from typing import Any
+
+import torch
+from torch import Tensor
+from torch.optim import Optimizer
+
+from dionw_b200._adamw import adamw_step, init_adamw_state
+from dionw_b200._buckets import Bucket, block_shape, build_buckets
+from dionw_b200._keys import (
+    EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, NEWTON_SCHULZ_KEY,
+    NUM_HEADS_KEY, ROUTE_KEY, ROW_NORMALIZATION_KEY, STRUCTURAL_KEYS,
+)
+from dionw_b200._matrix_step import MAX_RUN_ELEMENTS, run_elements, step_run
+from dionw_b200.ema import EMAConfig, IntegratedEMAOptimizer, ProfileRegion, no_profile
+from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate, MomentumForm, RowNormalization
+from dionw_b200.newton_schulz import NewtonSchulz
+from dionw_b200.routing import RouteKind
+
+__all__ = ["MAX_RUN_ELEMENTS", "NEWTON_SCHULZ_KEY", "Dion", "step_run"]
+
+
+def _require_param(param: Tensor) -> None:
+    """float32 on CUDA, or raise (ValueError off CUDA, TypeError for another dtype)."""
+    if not param.is_cuda:
+        raise ValueError(f"Dion runs on CUDA devices, got a parameter on {param.device}")
+    if param.dtype != torch.float32:
+        raise TypeError(
+            f"Dion needs float32 parameters, got {param.dtype}: keep float32 master weights and run the "
+            "forward and backward in bfloat16 (autocast)")
+
+
+def _require_group(group: dict[str, Any]) -> None:
+    """Validate a fully-defaulted group.
+
+    Raises:
+        TypeError: Without a route (the group was not built by ``param_groups``).
+        ValueError: On unknown enum values, negative lr / weight decay, a bad
+            fraction, Nesterov with row selection, a vector in a matrix group, or
+            a head split that does not divide the rows.
+    """
+    if ROUTE_KEY not in group:
+        raise TypeError(
+            "Dion param groups need a route: build them with dionw.param_groups(model) instead of "
+            "passing parameters directly")
+    NewtonSchulz(group[NEWTON_SCHULZ_KEY])
+    RowNormalization(group[ROW_NORMALIZATION_KEY])
+    form = MomentumForm(group[MOMENTUM_FORM_KEY])
+    if float(group["lr"]) < 0.0 or float(group["weight_decay"]) < 0.0:
+        raise ValueError("a group's lr and weight_decay must be >= 0")
+    kind = RouteKind(group[ROUTE_KEY])
+    if kind is RouteKind.ADAMW:
+        return
+    if kind is not RouteKind.MATRIX:
+        raise RuntimeError(f"Unhandled RouteKind: {kind}")
+    fraction = float(group[FRACTION_KEY])
+    if not 0.0 < fraction <= 1.0:
+        raise ValueError(f"fraction must be in (0, 1], got {fraction}")
+    if form is MomentumForm.NESTEROV and fraction < 1.0:
+        raise ValueError(
+            f"Nesterov momentum needs every row per step, got fraction {fraction}: build the groups with "
+            "fraction=1.0 or use MomentumForm.HEAVY_BALL")
+    for param in group["params"]:
+        if param.ndim < 2:
+            raise ValueError(f"a matrix group holds a {param.ndim}-D parameter; route it to AdamW")
+        block_shape(param, group[NUM_HEADS_KEY])
+
+
+def _fill_legacy_keys(saved: list[dict[str, Any]]) -> list[dict[str, Any]]:
+    """Groups saved before the row-normalization / momentum-form options meant NorMuon + heavy ball."""
+    legacy = {
+        ROW_NORMALIZATION_KEY: RowNormalization.NORMUON.value,
+        MOMENTUM_FORM_KEY: MomentumForm.HEAVY_BALL.value,
+    }
+    return [{**legacy, **group} if ROUTE_KEY in group else group for group in saved]
+
+
+def _require_same_structure(saved: list[dict[str, Any]], current: list[dict[str, Any]]) -> None:
+    """torch's loader restores every group setting from the checkpoint; a changed route,
+    fraction, head split, iteration, normalization or momentum form must be refused instead.
+
+    Raises:
+        ValueError: On a different group count, a missing key, or a mismatch.
+    """
+    if len(saved) != len(current):
+        raise ValueError(f"Dion state has {len(saved)} param groups, the optimizer {len(current)}")
+    for index, (old, new) in enumerate(zip(saved, current)):
+        for key in STRUCTURAL_KEYS:
+            if key not in old:
+                raise ValueError(f"Dion state group {index} has no {key!r}: it was not saved by dionw.Dion")
+            if old[key] != new[key]:
+                raise ValueError(
+                    f"Dion state group {index} {key!r}: checkpoint={old[key]!r}, optimizer={new[key]!r}. "
+                    "Build the groups as the checkpoint was built to resume it.")
+
+
+class _DionCore(Optimizer):
+    """The matrix and AdamW updates over routed param groups (no EMA)."""
+
+    def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float, muon_beta2: float,
+                 betas: tuple[float, float], weight_decay: float, eps: float,
+                 matrix_update: MatrixUpdate) -> None:
+        if lr < 0.0 or weight_decay < 0.0 or eps <= 0.0:
+            raise ValueError("lr and weight_decay must be >= 0 and eps > 0")
+        for name, value in ((MOMENTUM_KEY, momentum), (MUON_BETA2_KEY, muon_beta2),
+                            ("beta1", betas[0]), ("beta2", betas[1])):
+            if not 0.0 <= value < 1.0:
+                raise ValueError(f"{name} must be in [0, 1), got {value}")
+        defaults = {
+            "lr": lr,
+            MOMENTUM_KEY: momentum,
+            MUON_BETA2_KEY: muon_beta2,
+            "betas": betas,
+            "weight_decay": weight_decay,
+            "eps": eps,
+            FRACTION_KEY: 1.0,
+            NUM_HEADS_KEY: None,
+            NEWTON_SCHULZ_KEY: matrix_update.newton_schulz.value,
+            ROW_NORMALIZATION_KEY: matrix_update.row_normalization.value,
+            MOMENTUM_FORM_KEY: matrix_update.momentum_form.value,
+        }
+        self._buckets: list[Bucket] | None = None
+        super().__init__(params, defaults)
+
+    def add_param_group(self, param_group: dict[str, Any]) -> None:
+        """Validate and add a group; matrix state is repacked on the next step.
+
+        Raises:
+            TypeError: Without a route, for unordered params (a set), or a non-float32 parameter.
+            ValueError: On an invalid route, iteration or fraction, or a parameter off CUDA.
+        """
+        members = param_group["params"]
+        if isinstance(members, set):
+            raise TypeError("Dion param group params must be ordered, not a set")
+        group = {**param_group, "params": [members] if isinstance(members, Tensor) else list(members)}
+        for param in group["params"]:
+            _require_param(param)
+        _require_group({**self.defaults, **group})
+        super().add_param_group(group)
+        self._buckets = None
+        # AdamW state exists from the start so that an integrated EMA tracks every
+        # parameter, also one that never gets a gradient; matrix state appears with
+        # the buckets at the first step.
+        if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
+            for param in group["params"]:
+                init_adamw_state(param, self.state[param])
+
+    def initialize_state(self, param: Tensor) -> None:
+        """Create a parameter's fresh state before its first step, without updating it.
+
+        Raises:
+            ValueError: If ``param`` is not in the optimizer.
+        """
+        owner = None
+        for group in self.param_groups:
+            if any(p is param for p in group["params"]):
+                owner = group
+                break
+        if owner is None:
+            raise ValueError("parameter is not in the optimizer")
+        kind = RouteKind(owner[ROUTE_KEY])
+        if kind is RouteKind.MATRIX:
+            self._ensure_buckets()
+        elif kind is RouteKind.ADAMW:
+            if EXP_AVG_STATE not in self.state[param]:
+                init_adamw_state(param, self.state[param])
+        else:
+            raise RuntimeError(f"Unhandled RouteKind: {kind}")
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        """Load a checkpoint; matrix state is repacked into buckets on the next step.
+
+        Raises:
+            ValueError: If the saved groups differ from the optimizer's in count or
+                in any structural key.
+        """
+        saved = _fill_legacy_keys(state_dict["param_groups"])
+        _require_same_structure(saved, self.param_groups)
+        super().load_state_dict({**state_dict, "param_groups": saved})
+        self._buckets = None
+
+    @torch.no_grad()
+    def step(self, closure: Callable[[], float] | None = None) -> float | None:
+        """Update every parameter that has a gradient; returns the closure's loss, if any."""
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for bucket in self._ensure_buckets():
+            self._step_bucket(bucket)
+        for group in self.param_groups:
+            if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
+                adamw_step(group, self.state)
+        return loss
+
+    def _ensure_buckets(self) -> list[Bucket]:
+        if self._buckets is None:
+            self._buckets = build_buckets(self.param_groups, self.state)
+        return self._buckets
+
+    def _step_bucket(self, bucket: Bucket) -> None:
+        """Step the bucket's parameters that have gradients, in runs of consecutive parameters.
+
+        A run ends at a parameter without a gradient or when it would exceed
+        ``MAX_RUN_ELEMENTS`` update elements (a larger parameter runs alone).
+        """
+        group = self.param_groups[bucket.group_index]
+        pending: list[int] = []
+        elements = 0
+        for position, param in enumerate(bucket.params):
+            size = run_elements(bucket, position)
+            if pending and (param.grad is None or elements + size > MAX_RUN_ELEMENTS):
+                step_run(bucket, pending, group, self.state)
+                pending, elements = [], 0
+            if param.grad is not None:
+                pending.append(position)
+                elements += size
+        if pending:
+            step_run(bucket, pending, group, self.state)
+
+
+class Dion(IntegratedEMAOptimizer, _DionCore):
+    """Dion on matrices, AdamW on the rest, with an optional integrated EMA.
+
+    Build the groups with ``param_groups(model)``.  ``lr`` is an AdamW-equivalent
+    learning rate for every parameter.
+
+    Args:
+        params: Groups from ``param_groups``.
+        lr: Learning rate.
+        momentum: Matrix momentum (error-feedback decay of selected rows).
+        muon_beta2: EMA decay of each row's squared update (NorMuon).
+        betas: AdamW betas of AdamW-routed parameters.
+        weight_decay: Decoupled weight decay of groups without their own.
+        eps: AdamW epsilon.
+        matrix_update: ``DION3_UPDATE`` (default) or ``MUON_UPDATE``.
+        ema: EMA schedule and placement, or None.
+        profile_region: Named profiling region entered around EMA work.
+
+    Raises:
+        TypeError: For groups without a route or non-float32 parameters.
+        ValueError: On out-of-range hyperparameters, Nesterov momentum with row
+            selection, or parameters off CUDA.
+    """
+
+    def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
+                 muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95),
+                 weight_decay: float = 0.0, eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE,
+                 ema: EMAConfig | None = None, profile_region: ProfileRegion = no_profile) -> None:
+        super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
+                         weight_decay=weight_decay, eps=eps, matrix_update=matrix_update)
+        self._init_integrated_ema(ema, profile_region)

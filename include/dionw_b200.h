@@ -47,6 +47,8 @@ extern "C" {
 void dionw_last_error(char* buffer, size_t size);
 /* Library version string. */
 const char* dionw_version(void);
+/* Kernels this library has launched in this process so far (all threads). */
+int64_t dionw_launch_count(void);
 /* Reads and clears the device status word (non-zero: a bounded wait inside a
  * kernel ran out).  Synchronises the device; meant for tests and diagnostics. */
 int dionw_device_status(int* status);

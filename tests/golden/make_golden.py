@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import importlib.metadata
 import inspect
+import json
 import sys
 from pathlib import Path
 
@@ -174,6 +175,29 @@ def _adamw_case() -> None:
     _save("adamw", record)
 
 
+def _routing_case(dionw) -> None:
+    """``param_groups`` of the reference on the modules of routing_models.py."""
+    sys.path.insert(0, str(HERE))
+    import routing_models  # noqa: PLC0415
+
+    out = {}
+    shapes = routing_models.Shapes()
+    out["shapes_default"] = routing_models.describe(
+        shapes, *dionw.param_groups(shapes, fraction=0.5, selection_min_dim=1024, min_matrix_dim=8))
+    out["shapes_select"] = routing_models.describe(
+        shapes, *dionw.param_groups(shapes, fraction=0.25, selection_min_dim=32, min_matrix_dim=8))
+    out["shapes_no_decay"] = routing_models.describe(
+        shapes, *dionw.param_groups(shapes, no_weight_decay=[shapes.bare, shapes.norm.weight]))
+    attention = routing_models.Attention(dionw.Route, dionw.RouteKind)
+    out["attention"] = routing_models.describe(
+        attention, *dionw.param_groups(attention, fraction=0.5, selection_min_dim=16))
+    routes = {attention.proj.weight: dionw.Route(dionw.RouteKind.MATRIX, fraction=1.0)}
+    out["attention_routes"] = routing_models.describe(
+        attention, *dionw.param_groups(attention, fraction=0.25, selection_min_dim=16, routes=routes))
+    (HERE / "routing.json").write_text(json.dumps(out, indent=1))
+    print("routing.json:", len(out), "cases")
+
+
 def main() -> None:
     torch.set_num_threads(1)  # one summation order for every run of this script
     dionw, matrix_step, plain = _import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
@@ -185,6 +209,7 @@ def main() -> None:
                steps=4, ema=dionw.EMAConfig(decay=0.9, device=dionw.EMADevice.CPU, pin_memory=False))
     _newton_schulz_case(dionw, plain)
     _adamw_case()
+    _routing_case(dionw)
 
 
 if __name__ == "__main__":
