@@ -19,6 +19,7 @@ from __future__ import annotations
 import math
 from collections.abc import Callable, Sequence
 from contextlib import AbstractContextManager, nullcontext
+from dataclasses import dataclass
 from typing import Any
 
 import torch
@@ -30,7 +31,7 @@ from dionw_b200._keys import MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, RO
 from dionw_b200.matrix_update import MomentumForm, RowNormalization
 from dionw_b200.newton_schulz import NativeOrthogonalizer, padded, run_iteration
 
-__all__ = ["MAX_RUN_ELEMENTS", "run_elements", "step_run"]
+__all__ = ["MAX_RUN_ELEMENTS", "apply_result", "prepare_run", "run_elements", "step_run"]
 
 ADAMW_UPDATE_RMS = 0.2        # update RMS of AdamW that matrix steps are matched to
 NEWTON_SCHULZ_EPS = 1e-8      # added to the Frobenius norm; independent of AdamW's eps
@@ -63,6 +64,39 @@ def step_size(bucket: Bucket, lr: float) -> float:
     return lr * ADAMW_UPDATE_RMS * math.sqrt(max(rows, cols)) * math.sqrt(min(rows, cols) / min(k, cols))
 
 
+@dataclass
+class RunResult:
+    """What the first four stages of a run leave for the last one.
+
+    ``orthogonal`` is the bf16 ``[count, k, ld]`` Newton-Schulz output, ``rowmap``
+    the ``[count, rows]`` position of each weight row in it (-1: not selected;
+    None: every row), ``denom`` the NorMuon divisor of each output row and
+    ``scale`` the factor of each block (restored norm x signed step size).
+    """
+
+    params: list[Tensor]
+    rows_per_tensor: list[int]
+    count: int
+    rows: int
+    k: int
+    cols: int
+    orthogonal: Tensor
+    rowmap: Tensor | None
+    denom: Tensor
+    scale: Tensor
+
+
+def exchange_plan(count: int, rows: int, k: int, cols: int, selecting: bool) -> _workspace.Plan:
+    """The buffers of a ``RunResult`` in the order they lie in the arena: everything another
+    replica needs to apply the run (2-byte update rows, row map, row divisors, block scales)."""
+    plan: _workspace.Plan = {"x": ((count, k, padded(cols)), torch.bfloat16)}
+    if selecting:
+        plan["rowmap"] = ((count, rows), torch.int32)
+    plan["denom"] = ((count * k,), torch.float32)
+    plan["scale"] = ((count,), torch.float32)
+    return plan
+
+
 def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], state: ParamState) -> None:
     """Apply one Dion step to bucket parameters ``positions`` (consecutive, all with gradients).
 
@@ -70,18 +104,29 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
         RuntimeError: If a parameter has no gradient.
     """
     del state  # momentum and variance are reached through the bucket's own buffers
+    apply_result(prepare_run(bucket, positions, group), group)
+
+
+def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
+                arena: str = "run") -> RunResult:
+    """Stages 1-4 of a run: everything except touching the weights.
+
+    The result's tensors live in the scratch arena ``arena`` of the bucket's device and
+    start with the entries of ``exchange_plan`` in that order.
+
+    Raises:
+        RuntimeError: If a parameter has no gradient.
+    """
     params = [bucket.params[i] for i in positions]
     grads: list[Tensor] = []
     for param in params:
         if param.grad is None:
             raise RuntimeError("a Dion run holds a parameter without a gradient")
         grads.append(param.grad)
-    # The kernels walk row-major memory: a channels-last gradient or weight is
-    # packed first (and the weight written back afterwards).
+    # The kernels walk row-major memory: a channels-last gradient is packed first.
     if len({g.dtype for g in grads}) > 1:
         grads = [g.float() for g in grads]
     grads = [g if g.is_contiguous() else g.contiguous() for g in grads]
-    targets = [p if p.is_contiguous() else p.detach().contiguous() for p in params]
 
     blocks = bucket.run_blocks(positions)
     count = blocks.stop - blocks.start
@@ -89,8 +134,7 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
     momentum = bucket.momentum[blocks]
     variance = bucket.variance[blocks].view(count, rows)
     rows_per_tensor = [(bucket.slices[i].stop - bucket.slices[i].start) * rows for i in positions]
-    lr = float(group["lr"])
-    step = -step_size(bucket, lr)
+    step = -step_size(bucket, float(group["lr"]))
     bucket.step_scale = step
     decay = float(group[MOMENTUM_KEY])
     selecting = k < rows
@@ -99,26 +143,24 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
     dtype = fn.dtype if native else torch.float16
     device = momentum.device
 
-    plan: dict[str, tuple[tuple[int, ...], torch.dtype]] = {
+    plan = exchange_plan(count, rows, k, cols, selecting)
+    plan["x"] = (plan["x"][0], dtype)  # the operand is iterated in place and ends as bf16
+    plan.update({
         "scores": ((count, rows), torch.float32),
         "sumsq": ((count, rows), torch.float32),
         "index": ((count, k), torch.int32),
-        "rowmap": ((count, rows), torch.int32),
         "frob": ((count,), torch.float32),
         "rowsq": ((count * k,), torch.float32),
-        "denom": ((count * k,), torch.float32),
-        "scale": ((count,), torch.float32),
-        "x": ((count, k, padded(cols)), dtype),
-    }
+    })
     if not selecting:
         plan["u"] = ((count, rows, cols), torch.float32)
     if native:
         plan["ns"] = ((fn.workspace_bytes(count, k, cols),), torch.uint8)
         if k > cols:
             plan["xt"] = ((count, cols, padded(k)), dtype)
-    buf = _workspace.carve(device, plan)
+    buf = _workspace.carve(device, plan, arena)
 
-    # 1-2: accumulate, select, decay, pack
+    # 1-2: accumulate, select
     if selecting:
         with _stage("accumulate"):
             _native.accumulate_row_l1_run(grads, rows_per_tensor, momentum, buf["scores"], buf["sumsq"], cols)
@@ -133,7 +175,7 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
             _native.block_norms(buf["sumsq"], buf["frob"])
         index, rowmap, source = None, None, buf["u"]
 
-    # 3: orthogonalize
+    # 3: decay + pack, orthogonalize
     if native:
         with _stage("pack"):
             _native.pack_rows(source, index, buf["frob"], k, buf["x"], decay=decay, decay_rows=selecting,
@@ -151,12 +193,20 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
         _native.normuon_rows(buf["rowsq"], variance, index, blocks=count, rows=rows, k=k, cols=cols,
                              weight=1.0 - float(group[MUON_BETA2_KEY]), eps=NORMALIZATION_EPS, step=step,
                              normalize=normalize, denom=buf["denom"], scale=buf["scale"])
+    return RunResult(params=params, rows_per_tensor=rows_per_tensor, count=count, rows=rows, k=k, cols=cols,
+                     orthogonal=orthogonal, rowmap=rowmap, denom=buf["denom"], scale=buf["scale"])
 
-    # 5: decay + update
-    weight_decay = float(group["weight_decay"])
+
+def apply_result(result: RunResult, group: dict[str, Any]) -> None:
+    """Stage 5: decoupled weight decay on every row, the scaled update on the selected rows."""
+    params = result.params
+    # A channels-last weight is updated through a packed copy and written back.
+    targets = [p if p.is_contiguous() else p.detach().contiguous() for p in params]
+    lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
     with _stage("apply"):
-        _native.apply_run(targets, rows_per_tensor, orthogonal, rowmap, buf["denom"], buf["scale"], rows=rows, k=k,
-                          cols=cols, decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0)
+        _native.apply_run(targets, result.rows_per_tensor, result.orthogonal, result.rowmap, result.denom,
+                          result.scale, rows=result.rows, k=result.k, cols=result.cols,
+                          decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0)
     for param, target in zip(params, targets):
         if target is not param:
             param.copy_(target)
