@@ -52,6 +52,8 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_newton_schulz_workspace_bytes": (c_size_t, (c_int64, c_int64, c_int64, c_int)),
     "dionw_newton_schulz": (
         c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p)),
+    "dionw_newton_schulz_static": (
+        c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p)),
     "dionw_symmetric_product": (
         c_int, (c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float, c_float, c_void_p, c_int64,
                 c_void_p, c_float, c_int, c_void_p)),
@@ -203,6 +205,16 @@ def newton_schulz(x: Tensor, out: Tensor, m: int, n: int, kind: int, workspace: 
     _check(library().dionw_newton_schulz(x.data_ptr(), out.data_ptr(), x.shape[0], m, n, x.stride(-2), kind,
                                          workspace.data_ptr(), workspace.numel() * workspace.element_size(),
                                          _stream(x)))
+
+
+STATIC_SCRATCH_BYTES = 64 << 20
+
+
+def newton_schulz_static(x: Tensor, out: Tensor, m: int, n: int, kind: int) -> None:
+    """``newton_schulz`` on the library's built-in 64 MiB scratch: no workspace argument, no
+    allocation.  Larger problems raise; calls that overlap on one GPU race on the scratch."""
+    _check(library().dionw_newton_schulz_static(x.data_ptr(), out.data_ptr(), x.shape[0], m, n, x.stride(-2),
+                                                kind, _stream(x)))
 
 
 def symmetric_product(a: Tensor, out: Tensor, *, cin: Tensor | None = None, alpha: float = 1.0,

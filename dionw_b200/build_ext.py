@@ -17,7 +17,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "lib" / "libdionw_b200.so"
-SOURCES = ("api.cu", "momentum.cu", "update.cu", "gemm.cu", "newton_schulz.cu")
+SOURCES = ("api.cu", "momentum.cu", "update.cu", "gemm.cu", "newton_schulz.cu", "newton_schulz_static.cu")
 FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-cudart", "static",

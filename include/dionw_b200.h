@@ -122,6 +122,25 @@ int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m, int64_t n
                         int64_t ldx, int kind, void* workspace, size_t workspace_bytes,
                         void* stream);
 
+/* The same iteration for callers that have no scratch to give: a host bound to
+ * this ABI without torch's allocator, a serving loop whose memory was budgeted at
+ * start-up, a process whose device memory already belongs to a framework's pool,
+ * a loop that may not stall on cudaMalloc/cudaFree.  The scratch is a fixed
+ * DIONW_STATIC_SCRATCH_BYTES (64 MiB) array inside the library image, held on
+ * every GPU the library is loaded on until the process exits; a problem whose
+ * dionw_newton_schulz_workspace_bytes() exceeds it is refused with
+ * DIONW_ERR_WORKSPACE.  The call allocates nothing.  Its first call on a device
+ * looks the array's device address up (cudaGetSymbolAddress, with the current
+ * device): make that call once per device during set-up, before any stream
+ * capture is begun.  All calls on a device share the one array, which keeps
+ * whatever the last call left in it (nothing needs clearing: each product writes
+ * its output whole before it is read); two calls that overlap on the GPU, e.g.
+ * on different streams, race on it.  Arguments as dionw_newton_schulz.
+ * This entry has no counterpart in the reference. */
+#define DIONW_STATIC_SCRATCH_BYTES (64u << 20)
+int dionw_newton_schulz_static(void* x, void* out, int64_t blocks, int64_t m, int64_t n,
+                               int64_t ldx, int kind, void* stream);
+
 /* C = alpha * A A^T + beta * Cin on the lower triangle of tiles, mirrored;
  * out2 (optional) = C + diag * I.  A is [blocks, m, lda] with kdim columns.
  * dtype F16 or BF16 for every operand.  ns_line_1 is alpha=1, beta=0, cin=NULL;
