@@ -1,0 +1,382 @@
+"""``ShardedDion``: the Dion step over several GPUs of one node.
+
+The reference is single-GPU by design (README.md:446-456 there); this is new
+design on top of the same kernels.  Weights and gradients are replicated on
+every rank (the state after a data-parallel gradient all-reduce).  What is
+sharded is the optimizer's work and state:
+
+* matrix parameters are dealt to ranks by Newton-Schulz cost (longest first, to
+  the least loaded rank); a rank keeps momentum and variance only for the
+  parameters it owns and runs stages 1-4 of the step (accumulate, select, pack,
+  orthogonalize, NorMuon scales) for them alone;
+* per round, ONE all-gather ships what a replica needs to apply a run: the bf16
+  update rows, the row map, the row divisors and the block scales (they lie
+  contiguously at the head of the run's scratch arena, so the arena is the send
+  buffer); every rank then applies every run to its replica of the weights with
+  the same kernel and the same inputs, so replicas stay bit-identical;
+* large AdamW tensors are cut into ``world`` equal element ranges: each rank
+  updates its range (moments exist only for it) and an in-place all-gather
+  rebuilds the parameter; small ones are updated on every rank.
+
+The all-gather of round t is in flight while round t+1 computes (two scratch
+arenas alternate).  Received data is in local memory before any kernel reads it;
+no kernel touches a peer's memory.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Callable, Iterable, Sequence
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+from torch import Tensor
+
+from dionw_b200 import _matrix_step, _native, _workspace
+from dionw_b200._adamw import init_adamw_state
+from dionw_b200._buckets import Bucket, block_shape, build_buckets
+from dionw_b200._keys import (
+    ADAMW_STEP_STATE, EXP_AVG_SQ_STATE, EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_STATE, NUM_HEADS_KEY, ROUTE_KEY,
+    VARIANCE_STATE,
+)
+from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate
+from dionw_b200.optimizer import _DionCore
+from dionw_b200.routing import RouteKind
+
+__all__ = ["ShardedDion", "assign_by_cost", "newton_schulz_cost", "shard_range", "split_runs"]
+
+# AdamW tensors at least this large are cut into per-rank element ranges.
+ADAMW_SHARD_MIN_ELEMENTS = 1 << 20
+
+
+# ---------------------------------------------------------------------------
+# host-side planning (pure functions; the same on every rank)
+# ---------------------------------------------------------------------------
+def newton_schulz_cost(rows: int, cols: int, k: int, blocks: int = 1) -> float:
+    """FLOPs of orthogonalizing ``blocks`` operands of ``k`` selected rows by ``cols`` columns."""
+    m, n = min(k, cols), max(k, cols)
+    per_block = 20.0 * m**3 if m == n else 2.0 * (3.0 * m * m * n + 11.5 * m**3)
+    return blocks * per_block
+
+
+def assign_by_cost(costs: Sequence[float], world: int) -> list[int]:
+    """Owner rank of each unit: longest processing time first, to the least loaded rank.
+
+    Ties go to the lower unit index and the lower rank, so every rank computes the same answer.
+    """
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    load = [0.0] * world
+    owner = [0] * len(costs)
+    for i in order:
+        rank = min(range(world), key=lambda r: (load[r], r))
+        owner[i] = rank
+        load[rank] += costs[i]
+    return owner
+
+
+def split_runs(sizes: Sequence[int | None], limit: int) -> list[list[int]]:
+    """Positions grouped into runs of consecutive entries, as ``_DionCore._step_bucket`` does.
+
+    ``sizes[i]`` is the update-element count of entry ``i``, or None when it has no gradient
+    (which ends the current run).  A run holds at most ``limit`` elements; a larger entry runs alone.
+    """
+    runs: list[list[int]] = []
+    current: list[int] = []
+    total = 0
+    for position, size in enumerate(sizes):
+        if current and (size is None or total + size > limit):
+            runs.append(current)
+            current, total = [], 0
+        if size is not None:
+            current.append(position)
+            total += size
+    if current:
+        runs.append(current)
+    return runs
+
+
+def shard_range(numel: int, rank: int, world: int) -> tuple[int, int]:
+    """Element range ``[start, stop)`` of ``rank`` when ``numel`` divides evenly by ``world``."""
+    per = numel // world
+    return rank * per, (rank + 1) * per
+
+
+@dataclass
+class _SharedBucket:
+    """Same-shape matrix parameters of one group across all ranks."""
+
+    group_index: int
+    rows: int
+    cols: int
+    k: int
+    params: list[Tensor]
+    blocks: list[int]           # blocks per parameter
+    owners: list[int]           # owner rank per parameter
+    local: Bucket | None = None  # this rank's slab (owned parameters only)
+
+
+@dataclass
+class _Round:
+    """One all-gather in flight: who contributed what, and where it lands."""
+
+    work: Any
+    recv: Tensor
+    slot: int
+    counts: list[int]
+    params: list[list[Tensor]]
+    blocks: list[list[int]]
+    bucket: _SharedBucket
+    group: dict[str, Any]
+
+
+class ShardedDion(_DionCore):
+    """``Dion`` with work and state sharded over the ranks of ``process_group``.
+
+    Same arguments as ``Dion`` (no EMA here).  Every rank must hold identical
+    parameters and, at each step, identical gradients; after the step the
+    parameters are again identical on every rank, and equal bit for bit to what
+    a single-GPU ``Dion`` computes.  ``state_dict()`` returns the single-GPU
+    layout on every rank (it gathers); ``load_state_dict()`` takes that layout.
+    """
+
+    def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
+                 muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.0,
+                 eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE, process_group: Any = None) -> None:
+        import torch.distributed as dist
+
+        if not dist.is_initialized():
+            raise RuntimeError("ShardedDion needs torch.distributed to be initialised (one process per GPU)")
+        self._dist = dist
+        self._pg = process_group
+        self._world = dist.get_world_size(process_group)
+        self._rank = dist.get_rank(process_group)
+        self._shared: list[_SharedBucket] | None = None
+        super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
+                         weight_decay=weight_decay, eps=eps, matrix_update=matrix_update)
+
+    # ---- layout --------------------------------------------------------------
+    def _is_cut(self, param: Tensor) -> bool:
+        """Whether an AdamW tensor is updated by element range rather than whole on every rank."""
+        n = param.numel()
+        return self._world > 1 and n >= ADAMW_SHARD_MIN_ELEMENTS and n % self._world == 0 and param.is_contiguous()
+
+    def _new_adamw_state(self, param: Tensor) -> None:
+        entry = self.state[param]
+        if not self._is_cut(param):
+            init_adamw_state(param, entry)
+            return
+        per = param.numel() // self._world
+        entry[EXP_AVG_STATE] = torch.zeros(per, dtype=param.dtype, device=param.device)
+        entry[EXP_AVG_SQ_STATE] = torch.zeros(per, dtype=param.dtype, device=param.device)
+        entry[ADAMW_STEP_STATE] = torch.zeros((), dtype=torch.float32, device=param.device)
+
+    def add_param_group(self, param_group: dict[str, Any]) -> None:
+        super().add_param_group(param_group)
+        self._shared = None
+
+    def owners(self) -> dict[Tensor, int]:
+        """Owner rank of every matrix parameter."""
+        return {p: o for sb in self._ensure_shared() for p, o in zip(sb.params, sb.owners)}
+
+    def _ensure_shared(self) -> list[_SharedBucket]:
+        if self._shared is not None:
+            return self._shared
+        units: list[tuple[int, Tensor, int, int, int, int]] = []
+        for gi, group in enumerate(self.param_groups):
+            if RouteKind(group[ROUTE_KEY]) is not RouteKind.MATRIX:
+                continue
+            for param in group["params"]:
+                blocks, rows, cols = block_shape(param, group[NUM_HEADS_KEY])
+                k = min(rows, math.ceil(float(group[FRACTION_KEY]) * rows))
+                units.append((gi, param, blocks, rows, cols, k))
+        owners = assign_by_cost([newton_schulz_cost(r, c, k, b) for _, _, b, r, c, k in units], self._world)
+        shared: dict[tuple, _SharedBucket] = {}
+        owned: dict[int, list[Tensor]] = {}
+        for (gi, param, blocks, rows, cols, k), owner in zip(units, owners):
+            sb = shared.setdefault((gi, rows, cols, param.device),
+                                   _SharedBucket(gi, rows, cols, k, [], [], []))
+            sb.params.append(param)
+            sb.blocks.append(blocks)
+            sb.owners.append(owner)
+            if owner == self._rank:
+                owned.setdefault(gi, []).append(param)
+        filtered = [
+            {**group, "params": owned.get(gi, [])} if RouteKind(group[ROUTE_KEY]) is RouteKind.MATRIX else group
+            for gi, group in enumerate(self.param_groups)
+        ]
+        for bucket in build_buckets(filtered, self.state):
+            shared[(bucket.group_index, bucket.rows, bucket.cols, bucket.params[0].device)].local = bucket
+        mine = {id(p) for ps in owned.values() for p in ps}
+        for sb in shared.values():
+            for param in sb.params:  # a loaded checkpoint leaves full state everywhere: keep the owner's only
+                if id(param) not in mine and param in self.state:
+                    self.state[param].pop(MOMENTUM_STATE, None)
+                    self.state[param].pop(VARIANCE_STATE, None)
+        self._shared = list(shared.values())
+        self._buckets = [sb.local for sb in self._shared if sb.local is not None]
+        return self._shared
+
+    def _ensure_buckets(self) -> list[Bucket]:
+        self._ensure_shared()
+        return self._buckets or []
+
+    # ---- the step ------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, closure: Callable[[], float] | None = None) -> float | None:
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        gathers = self._step_adamw()
+        self._step_matrices()
+        for work in gathers:
+            work.wait()
+        return loss
+
+    def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
+        return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
+
+    def _step_matrices(self) -> None:
+        import dionw_b200.optimizer as optimizer_module  # MAX_RUN_ELEMENTS is looked up at call time
+
+        limit = optimizer_module.MAX_RUN_ELEMENTS
+        world, me = self._world, self._rank
+        pending: _Round | None = None
+        round_id = 0
+        for sb in self._ensure_shared():
+            group = self.param_groups[sb.group_index]
+            selecting = sb.k < sb.rows
+            device = sb.params[0].device
+            per_rank = [[i for i, o in enumerate(sb.owners) if o == r] for r in range(world)]
+            runs = []
+            for members in per_rank:
+                sizes = [None if sb.params[i].grad is None else sb.blocks[i] * sb.k * sb.cols for i in members]
+                runs.append([[members[j] for j in run] for run in split_runs(sizes, limit)])
+            for t in range(max((len(r) for r in runs), default=0)):
+                chosen = [r[t] if t < len(r) else [] for r in runs]
+                counts = [sum(sb.blocks[i] for i in c) for c in chosen]
+                slot = max(_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, selecting))[1]
+                           if c else 0 for c in counts)
+                name = f"run{round_id % 2}"
+                _workspace.arena(device, slot, name)
+                if chosen[me]:
+                    local_index = {id(p): j for j, p in enumerate(sb.local.params)}
+                    positions = [local_index[id(sb.params[i])] for i in chosen[me]]
+                    _matrix_step.prepare_run(sb.local, positions, group, arena=name)
+                send = _workspace.arena(device, slot, name)[:slot]
+                if world == 1:
+                    recv, work = send, None
+                else:
+                    recv = _workspace.arena(device, slot * world, f"recv{round_id % 2}")[: slot * world]
+                    work = self._all_gather(recv, send)
+                issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
+                                [[sb.blocks[i] for i in c] for c in chosen], sb, group)
+                if pending is not None:
+                    self._apply_round(pending)
+                pending = issued
+                round_id += 1
+        if pending is not None:
+            self._apply_round(pending)
+
+    def _apply_round(self, rnd: _Round) -> None:
+        if rnd.work is not None:
+            rnd.work.wait()
+        sb = rnd.bucket
+        selecting = sb.k < sb.rows
+        for rank, count in enumerate(rnd.counts):
+            if count == 0:
+                continue
+            got = _workspace.views(rnd.recv, _matrix_step.exchange_plan(count, sb.rows, sb.k, sb.cols, selecting),
+                                   base=rank * rnd.slot)
+            result = _matrix_step.RunResult(
+                params=rnd.params[rank], rows_per_tensor=[b * sb.rows for b in rnd.blocks[rank]], count=count,
+                rows=sb.rows, k=sb.k, cols=sb.cols, orthogonal=got["x"], rowmap=got.get("rowmap"),
+                denom=got["denom"], scale=got["scale"])
+            _matrix_step.apply_result(result, rnd.group)
+
+    def _step_adamw(self) -> list[Any]:
+        gathers: list[Any] = []
+        for group in self.param_groups:
+            if RouteKind(group[ROUTE_KEY]) is not RouteKind.ADAMW:
+                continue
+            lists: tuple[list[Tensor], ...] = ([], [], [], [], [])
+            rebuilt: list[tuple[Tensor, Tensor]] = []
+            for param in group["params"]:
+                grad = param.grad
+                if grad is None:
+                    continue
+                entry = self.state[param]
+                if EXP_AVG_STATE not in entry:
+                    self._new_adamw_state(param)
+                if grad.dtype is not torch.float32 or not grad.is_contiguous():
+                    grad = grad.float().contiguous()
+                target, source = param, grad
+                if self._is_cut(param):
+                    start, stop = shard_range(param.numel(), self._rank, self._world)
+                    target, source = param.view(-1)[start:stop], grad.view(-1)[start:stop]
+                    rebuilt.append((param.view(-1), target))
+                elif not param.is_contiguous():
+                    raise NotImplementedError("ShardedDion needs contiguous AdamW parameters")
+                for store, value in zip(lists, (target, source, entry[EXP_AVG_STATE], entry[EXP_AVG_SQ_STATE],
+                                                entry[ADAMW_STEP_STATE])):
+                    store.append(value)
+            if not lists[0]:
+                continue
+            beta1, beta2 = group["betas"]
+            with _matrix_step._stage("adamw"):
+                _native.adamw_multi(*lists, lr=float(group["lr"]), beta1=float(beta1), beta2=float(beta2),
+                                    weight_decay=float(group["weight_decay"]), eps=float(group["eps"]))
+            gathers.extend(self._all_gather(whole, piece) for whole, piece in rebuilt)
+        return gathers
+
+    # ---- checkpoints ---------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        """The single-GPU layout, on every rank: owners broadcast their momentum and variance,
+        cut AdamW moments are gathered.  A collective call: every rank must make it."""
+        packed = super().state_dict()
+        dist = self._dist
+        owners = self.owners()
+        index = 0
+        for group in self.param_groups:
+            matrix = RouteKind(group[ROUTE_KEY]) is RouteKind.MATRIX
+            for param in group["params"]:
+                entry = dict(packed["state"].get(index, {}))
+                if matrix and param in owners:
+                    owner = owners[param]
+                    if owner == self._rank:
+                        momentum = self.state[param][MOMENTUM_STATE].clone()
+                        variance = self.state[param][VARIANCE_STATE].clone()
+                    else:
+                        momentum = torch.empty_like(param)
+                        variance = torch.empty(param.shape[0], 1, dtype=param.dtype, device=param.device)
+                    if self._world > 1:
+                        src = dist.get_global_rank(self._pg, owner) if self._pg is not None else owner
+                        dist.broadcast(momentum, src=src, group=self._pg)
+                        dist.broadcast(variance, src=src, group=self._pg)
+                    entry[MOMENTUM_STATE], entry[VARIANCE_STATE] = momentum, variance
+                elif not matrix and self._is_cut(param) and EXP_AVG_STATE in self.state.get(param, {}):
+                    for key in (EXP_AVG_STATE, EXP_AVG_SQ_STATE):
+                        whole = torch.empty_like(param)
+                        dist.all_gather_into_tensor(whole.view(-1), self.state[param][key], group=self._pg)
+                        entry[key] = whole
+                if entry:
+                    packed["state"][index] = entry
+                index += 1
+        return packed
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        """Takes the single-GPU layout; each rank keeps its own share of it."""
+        super().load_state_dict(state_dict)
+        self._shared = None
+        for group in self.param_groups:
+            if RouteKind(group[ROUTE_KEY]) is not RouteKind.ADAMW:
+                continue
+            for param in group["params"]:
+                entry = self.state.get(param)
+                if not entry or EXP_AVG_STATE not in entry or not self._is_cut(param):
+                    continue
+                start, stop = shard_range(param.numel(), self._rank, self._world)
+                for key in (EXP_AVG_STATE, EXP_AVG_SQ_STATE):
+                    if entry[key].numel() == param.numel():
+                        entry[key] = entry[key].reshape(-1)[start:stop].clone()

@@ -160,7 +160,11 @@ class _DionCore(Optimizer):
         # the buckets at the first step.
         if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
             for param in group["params"]:
-                init_adamw_state(param, self.state[param])
+                self._new_adamw_state(param)
+
+    def _new_adamw_state(self, param: Tensor) -> None:
+        """Fresh AdamW moments and step counter for ``param`` (a sharded optimizer keeps less)."""
+        init_adamw_state(param, self.state[param])
 
     def initialize_state(self, param: Tensor) -> None:
         """Create a parameter's fresh state before its first step, without updating it.
@@ -180,7 +184,7 @@ class _DionCore(Optimizer):
             self._ensure_buckets()
         elif kind is RouteKind.ADAMW:
             if EXP_AVG_STATE not in self.state[param]:
-                init_adamw_state(param, self.state[param])
+                self._new_adamw_state(param)
         else:
             raise RuntimeError(f"Unhandled RouteKind: {kind}")
 

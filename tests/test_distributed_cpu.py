@@ -1,0 +1,89 @@
+"""Host logic of the sharded step, on CPU: the planning functions, and the byte-level
+exchange of run results between two ``gloo`` ranks (the same layout arithmetic and the same
+collective call the GPU path uses; the kernels themselves need a GPU)."""
+
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from dionw_b200 import _matrix_step, _workspace
+from dionw_b200.distributed import assign_by_cost, newton_schulz_cost, shard_range, split_runs
+
+
+def test_cost_model_counts_the_gram_schedule() -> None:
+    assert newton_schulz_cost(14336, 4096, 3584) == 2 * (3 * 3584**2 * 4096 + 11.5 * 3584**3)
+    assert newton_schulz_cost(768, 768, 768) == 20 * 768**3
+    assert newton_schulz_cost(3072, 768, 3072) == newton_schulz_cost(768, 3072, 768)  # tall == its transpose
+    assert newton_schulz_cost(64, 32, 64, blocks=3) == 3 * newton_schulz_cost(64, 32, 64)
+
+
+def test_llama8b_blocks_balance_perfectly_over_8_ranks() -> None:
+    layer = [(4096, 4096, 1024), (1024, 4096, 256), (1024, 4096, 256), (4096, 4096, 1024),
+             (14336, 4096, 3584), (14336, 4096, 3584), (4096, 14336, 1024)]
+    costs = [newton_schulz_cost(r, c, k) for _ in range(32) for r, c, k in layer]
+    owners = assign_by_cost(costs, 8)
+    load = [sum(c for c, o in zip(costs, owners) if o == rank) for rank in range(8)]
+    assert max(load) == pytest.approx(min(load), rel=1e-12)
+    assert assign_by_cost(costs, 8) == owners  # deterministic
+    assert assign_by_cost([3.0, 3.0, 3.0], 2) == [0, 1, 0]  # ties: lower unit first, lower rank first
+
+
+def test_split_runs_follows_the_single_gpu_rule() -> None:
+    assert split_runs([4, 4, None, 4, 9, 1], 8) == [[0, 1], [3], [4], [5]]
+    assert split_runs([None, None], 8) == []
+    assert split_runs([100], 8) == [[0]]  # an oversized entry still runs, alone
+    assert split_runs([3, 3, 3], 9) == [[0, 1, 2]]
+    assert shard_range(128256 * 4096, 3, 8) == (3 * 65667072, 4 * 65667072)
+
+
+def _exchange_worker(rank: int, world: int, port: int, failures) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows, k, cols = 48, 12, 40
+        counts = [3, 1]  # rank 0 contributes a run of 3 blocks, rank 1 a run of 1
+        plans = [_matrix_step.exchange_plan(c, rows, k, cols, True) for c in counts]
+        slot = max(_workspace.layout(p)[1] for p in plans)
+        arena = torch.zeros(slot + 4096, dtype=torch.uint8)
+        mine = _workspace.views(arena, plans[rank])
+        mine["x"].fill_(1.0 + rank)
+        mine["rowmap"].copy_(torch.arange(counts[rank] * rows, dtype=torch.int32).view(counts[rank], rows) + 1000 * rank)
+        mine["denom"].fill_(0.5 + rank)
+        mine["scale"].fill_(-0.25 - rank)
+        recv = torch.empty(slot * world, dtype=torch.uint8)
+        dist.all_gather_into_tensor(recv, arena[:slot])
+        for src in range(world):
+            got = _workspace.views(recv, plans[src], base=src * slot)
+            assert got["x"].shape == (counts[src], k, 40) and got["x"].dtype == torch.bfloat16
+            assert bool((got["x"] == 1.0 + src).all())
+            assert int(got["rowmap"][0, 5]) == 5 + 1000 * src and got["rowmap"].shape == (counts[src], rows)
+            assert bool((got["denom"] == 0.5 + src).all()) and got["denom"].numel() == counts[src] * k
+            assert bool((got["scale"] == -0.25 - src).all()) and got["scale"].numel() == counts[src]
+        # in-place gather of a cut AdamW tensor: every rank ends with every range
+        whole = torch.full((10,), -1.0)
+        start, stop = shard_range(10, rank, world)
+        whole[start:stop] = float(rank)
+        dist.all_gather_into_tensor(whole, whole[start:stop].clone())
+        assert whole.tolist() == [0.0] * 5 + [1.0] * 5
+    except Exception as exc:  # reported to the parent
+        failures.put(f"rank {rank}: {exc!r}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_exchange_run_results_over_gloo() -> None:
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert failures.empty(), failures.get()

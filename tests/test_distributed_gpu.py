@@ -1,0 +1,103 @@
+"""``ShardedDion`` on 2 GPUs against single-GPU ``Dion``: same bits in the weights after
+every step, the same checkpoint, and a resume from it.  Skipped with fewer than 2 GPUs."""
+
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(128, 256)] * 5 + [(512, 128)] * 3 + [(96, 96)] * 2
+
+
+def _model(device) -> nn.Module:
+    torch.manual_seed(0)
+    net = nn.Module()
+    net.mats = nn.ParameterList([nn.Parameter(torch.randn(s) * 0.02) for s in SHAPES])
+    net.big = nn.Embedding(4096, 512)          # 2 M elements: cut into per-rank ranges
+    net.norm = nn.Parameter(torch.randn(256) * 0.02)
+    return net.to(device)
+
+
+def _grads(net, step: int) -> None:
+    gen = torch.Generator().manual_seed(100 + step)
+    for i, p in enumerate(net.parameters()):
+        p.grad = None if (step == 1 and i == 2) else (torch.randn(p.shape, generator=gen) * 1e-3).to(p.device)
+
+
+def _worker(rank: int, world: int, port: int, failures) -> None:
+    import torch.distributed as dist
+
+    import dionw_b200 as dionw
+    from dionw_b200.distributed import ShardedDion
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        import dionw_b200.optimizer as optimizer_module
+        optimizer_module.MAX_RUN_ELEMENTS = 3 * 32 * 256  # several rounds per bucket, uneven run lengths
+
+        def build(cls, **kw):
+            net = _model(device)
+            groups, _ = dionw.param_groups(net, fraction=0.25, selection_min_dim=128)
+            return net, cls(groups, lr=3e-4, weight_decay=0.05, **kw)
+
+        single_net, single = build(dionw.Dion)
+        sharded_net, sharded = build(ShardedDion)
+        owners = sharded.owners()
+        assert {0, 1} == set(owners.values())
+        for step in range(3):
+            _grads(single_net, step)
+            _grads(sharded_net, step)
+            single.step()
+            sharded.step()
+            for a, b in zip(single_net.parameters(), sharded_net.parameters()):
+                assert torch.equal(a, b), f"step {step}: weights differ"
+        # state lives with the owner only
+        for p, owner in owners.items():
+            assert ("momentum" in sharded.state[p]) == (owner == rank)
+        assert sharded.state[sharded_net.big.weight]["exp_avg"].numel() == 4096 * 512 // world
+        # the gathered checkpoint equals the single-GPU one
+        want, got = single.state_dict(), sharded.state_dict()
+        assert want["param_groups"] == got["param_groups"]
+        assert set(want["state"]) == set(got["state"])
+        for index, entry in want["state"].items():
+            for key, value in entry.items():
+                assert torch.equal(value, got["state"][index][key]), (index, key)
+        # resume: a fresh sharded optimizer loaded from it continues identically
+        resumed_net, resumed = build(ShardedDion)
+        resumed_net.load_state_dict(sharded_net.state_dict())
+        resumed.load_state_dict({**got, "state": {i: {k: v.clone() for k, v in e.items()}
+                                                  for i, e in got["state"].items()}})
+        for net, opt in ((single_net, single), (resumed_net, resumed)):
+            _grads(net, 3)
+            opt.step()
+        for a, b in zip(single_net.parameters(), resumed_net.parameters()):
+            assert torch.equal(a, b), "resumed weights differ"
+        torch.cuda.synchronize()
+    except Exception as exc:  # reported to the parent
+        import traceback
+        failures.put(f"rank {rank}: {exc!r}\n{traceback.format_exc()}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_step_equals_single_gpu_step() -> None:
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    assert failures.empty(), failures.get()
+    assert all(p.exitcode == 0 for p in procs)
