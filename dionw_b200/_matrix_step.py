@@ -31,7 +31,8 @@ from dionw_b200._keys import MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, RO
 from dionw_b200.matrix_update import MomentumForm, RowNormalization
 from dionw_b200.newton_schulz import NativeOrthogonalizer, padded, run_iteration
 
-__all__ = ["MAX_RUN_ELEMENTS", "apply_result", "prepare_run", "run_elements", "step_run"]
+__all__ = ["MAX_RUN_ELEMENTS", "apply_result", "open_run", "prepare_run", "run_core", "run_elements",
+           "run_front", "step_run"]
 
 ADAMW_UPDATE_RMS = 0.2        # update RMS of AdamW that matrix steps are matched to
 NEWTON_SCHULZ_EPS = 1e-8      # added to the Frobenius norm; independent of AdamW's eps
@@ -107,12 +108,33 @@ def step_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], st
     apply_result(prepare_run(bucket, positions, group), group)
 
 
-def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
-                arena: str = "run") -> RunResult:
-    """Stages 1-4 of a run: everything except touching the weights.
+@dataclass
+class RunContext:
+    """A run between its stages: the tensors it reads and the scratch it owns."""
 
-    The result's tensors live in the scratch arena ``arena`` of the bucket's device and
-    start with the entries of ``exchange_plan`` in that order.
+    bucket: Bucket
+    group: dict[str, Any]
+    params: list[Tensor]
+    grads: list[Tensor]
+    rows_per_tensor: list[int]
+    count: int
+    momentum: Tensor
+    variance: Tensor
+    step: float
+    buf: dict[str, Tensor]
+    index: Tensor | None = None
+    rowmap: Tensor | None = None
+    source: Tensor | None = None
+
+    @property
+    def selecting(self) -> bool:
+        return self.bucket.selected_rows < self.bucket.rows
+
+
+def open_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], arena: str = "run") -> RunContext:
+    """Host-side set-up of a run: checks the gradients and carves the run's scratch from ``arena``.
+
+    The scratch starts with the entries of ``exchange_plan`` in that order.
 
     Raises:
         RuntimeError: If a parameter has no gradient.
@@ -131,17 +153,12 @@ def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
     blocks = bucket.run_blocks(positions)
     count = blocks.stop - blocks.start
     rows, cols, k = bucket.rows, bucket.cols, bucket.selected_rows
-    momentum = bucket.momentum[blocks]
-    variance = bucket.variance[blocks].view(count, rows)
-    rows_per_tensor = [(bucket.slices[i].stop - bucket.slices[i].start) * rows for i in positions]
     step = -step_size(bucket, float(group["lr"]))
     bucket.step_scale = step
-    decay = float(group[MOMENTUM_KEY])
     selecting = k < rows
     fn = bucket.orthogonalize
     native = isinstance(fn, NativeOrthogonalizer)
     dtype = fn.dtype if native else torch.float16
-    device = momentum.device
 
     plan = exchange_plan(count, rows, k, cols, selecting)
     plan["x"] = (plan["x"][0], dtype)  # the operand is iterated in place and ends as bf16
@@ -158,43 +175,68 @@ def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
         plan["ns"] = ((fn.workspace_bytes(count, k, cols),), torch.uint8)
         if k > cols:
             plan["xt"] = ((count, cols, padded(k)), dtype)
-    buf = _workspace.carve(device, plan, arena)
+    momentum = bucket.momentum[blocks]
+    return RunContext(
+        bucket=bucket, group=group, params=params, grads=grads,
+        rows_per_tensor=[(bucket.slices[i].stop - bucket.slices[i].start) * rows for i in positions],
+        count=count, momentum=momentum, variance=bucket.variance[blocks].view(count, rows), step=step,
+        buf=_workspace.carve(momentum.device, plan, arena))
 
-    # 1-2: accumulate, select
-    if selecting:
+
+def run_front(ctx: RunContext) -> None:
+    """Stages 1-2 and the pack: the HBM-bound front of a run (reads G, updates M, writes the operand)."""
+    bucket, group, buf = ctx.bucket, ctx.group, ctx.buf
+    cols, k = bucket.cols, bucket.selected_rows
+    decay = float(group[MOMENTUM_KEY])
+    if ctx.selecting:
         with _stage("accumulate"):
-            _native.accumulate_row_l1_run(grads, rows_per_tensor, momentum, buf["scores"], buf["sumsq"], cols)
+            _native.accumulate_row_l1_run(ctx.grads, ctx.rows_per_tensor, ctx.momentum, buf["scores"],
+                                          buf["sumsq"], cols)
         with _stage("select"):
             _native.select_rows(buf["scores"], buf["sumsq"], k, buf["index"], buf["rowmap"], buf["frob"])
-        index, rowmap, source = buf["index"], buf["rowmap"], momentum
+        ctx.index, ctx.rowmap, ctx.source = buf["index"], buf["rowmap"], ctx.momentum
     else:
         nesterov = MomentumForm(group[MOMENTUM_FORM_KEY]) is MomentumForm.NESTEROV
         with _stage("accumulate"):
-            _native.accumulate_copy_decay_run(grads, rows_per_tensor, momentum, buf["u"], buf["sumsq"], cols, decay,
-                                              nesterov)
+            _native.accumulate_copy_decay_run(ctx.grads, ctx.rows_per_tensor, ctx.momentum, buf["u"],
+                                              buf["sumsq"], cols, decay, nesterov)
             _native.block_norms(buf["sumsq"], buf["frob"])
-        index, rowmap, source = None, None, buf["u"]
-
-    # 3: decay + pack, orthogonalize
-    if native:
+        ctx.index, ctx.rowmap, ctx.source = None, None, buf["u"]
+    fn = bucket.orthogonalize
+    if isinstance(fn, NativeOrthogonalizer):
         with _stage("pack"):
-            _native.pack_rows(source, index, buf["frob"], k, buf["x"], decay=decay, decay_rows=selecting,
-                              eps=NEWTON_SCHULZ_EPS, norm_scale=fn.norm_scale)
+            _native.pack_rows(ctx.source, ctx.index, buf["frob"], k, buf["x"], decay=decay,
+                              decay_rows=ctx.selecting, eps=NEWTON_SCHULZ_EPS, norm_scale=fn.norm_scale)
+
+
+def run_core(ctx: RunContext) -> RunResult:
+    """Stages 3-4: the tensor-core part (Newton-Schulz) and the NorMuon scales."""
+    bucket, group, buf = ctx.bucket, ctx.group, ctx.buf
+    rows, cols, k = bucket.rows, bucket.cols, bucket.selected_rows
+    fn = bucket.orthogonalize
+    if isinstance(fn, NativeOrthogonalizer):
         with _stage("newton_schulz"):
             orthogonal = run_iteration(fn, buf["x"], k, cols, buf["ns"], buf.get("xt"))
     else:
-        orthogonal = _foreign_orthogonalize(fn, source, index, decay, selecting, buf["x"])
-
-    # 4: row and block scales
+        orthogonal = _foreign_orthogonalize(fn, ctx.source, ctx.index, float(group[MOMENTUM_KEY]), ctx.selecting,
+                                            buf["x"])
     normalize = RowNormalization(group[ROW_NORMALIZATION_KEY]) is RowNormalization.NORMUON
     with _stage("finish"):
         if normalize:
             _native.row_sumsq_bf16(orthogonal, cols, buf["rowsq"])
-        _native.normuon_rows(buf["rowsq"], variance, index, blocks=count, rows=rows, k=k, cols=cols,
-                             weight=1.0 - float(group[MUON_BETA2_KEY]), eps=NORMALIZATION_EPS, step=step,
+        _native.normuon_rows(buf["rowsq"], ctx.variance, ctx.index, blocks=ctx.count, rows=rows, k=k, cols=cols,
+                             weight=1.0 - float(group[MUON_BETA2_KEY]), eps=NORMALIZATION_EPS, step=ctx.step,
                              normalize=normalize, denom=buf["denom"], scale=buf["scale"])
-    return RunResult(params=params, rows_per_tensor=rows_per_tensor, count=count, rows=rows, k=k, cols=cols,
-                     orthogonal=orthogonal, rowmap=rowmap, denom=buf["denom"], scale=buf["scale"])
+    return RunResult(params=ctx.params, rows_per_tensor=ctx.rows_per_tensor, count=ctx.count, rows=rows, k=k,
+                     cols=cols, orthogonal=orthogonal, rowmap=ctx.rowmap, denom=buf["denom"], scale=buf["scale"])
+
+
+def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
+                arena: str = "run") -> RunResult:
+    """Stages 1-4 of a run, one after the other on the current stream."""
+    ctx = open_run(bucket, positions, group, arena)
+    run_front(ctx)
+    return run_core(ctx)
 
 
 def apply_result(result: RunResult, group: dict[str, Any]) -> None:

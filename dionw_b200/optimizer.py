@@ -28,13 +28,19 @@ from dionw_b200._keys import (
     EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, NEWTON_SCHULZ_KEY,
     NUM_HEADS_KEY, ROUTE_KEY, ROW_NORMALIZATION_KEY, STRUCTURAL_KEYS,
 )
-from dionw_b200._matrix_step import MAX_RUN_ELEMENTS, run_elements, step_run
+from dionw_b200._matrix_step import (
+    MAX_RUN_ELEMENTS, apply_result, open_run, run_core, run_elements, run_front, step_run,
+)
 from dionw_b200.ema import EMAConfig, IntegratedEMAOptimizer, ProfileRegion, no_profile
 from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate, MomentumForm, RowNormalization
 from dionw_b200.newton_schulz import NewtonSchulz
 from dionw_b200.routing import RouteKind
 
 __all__ = ["MAX_RUN_ELEMENTS", "NEWTON_SCHULZ_KEY", "Dion", "step_run"]
+
+# ``step_run`` is a module attribute so that it can be replaced; the overlapped step only
+# takes over while it is still this function.
+_sequential_step_run = step_run
 
 
 def _require_param(param: Tensor) -> None:
@@ -137,6 +143,7 @@ class _DionCore(Optimizer):
             MOMENTUM_FORM_KEY: matrix_update.momentum_form.value,
         }
         self._buckets: list[Bucket] | None = None
+        self._side_streams: dict[torch.device, torch.cuda.Stream] = {}
         super().__init__(params, defaults)
 
     def add_param_group(self, param_group: dict[str, Any]) -> None:
@@ -207,37 +214,92 @@ class _DionCore(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        for bucket in self._ensure_buckets():
-            self._step_bucket(bucket)
+        runs = [(bucket, run) for bucket in self._ensure_buckets() for run in self._runs_of(bucket)]
+        devices = {bucket.momentum.device for bucket, _ in runs}
+        if self.overlap_streams and len(runs) > 1 and len(devices) == 1 and step_run is _sequential_step_run:
+            self._step_overlapped(runs, devices.pop())
+        else:
+            for bucket, run in runs:
+                step_run(bucket, run, self.param_groups[bucket.group_index], self.state)
+            self._step_adamw_groups()
+        return loss
+
+    def _step_adamw_groups(self) -> None:
         for group in self.param_groups:
             if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
                 adamw_step(group, self.state)
-        return loss
+
+    # Two streams per step: the tensor-core part of run i (Newton-Schulz, on the
+    # caller's stream) overlaps the HBM-bound parts of its neighbours on a side
+    # stream: accumulate/select/pack of run i+1, the weight update of run i-1,
+    # and AdamW.  Three scratch arenas rotate.  The arithmetic and its order per
+    # run are unchanged, so results are bit-identical to the sequential step.
+    overlap_streams = True
+
+    def _step_overlapped(self, runs: list[tuple[Bucket, list[int]]], device: torch.device) -> None:
+        main = torch.cuda.current_stream(device)
+        side = self._side_streams.get(device)
+        if side is None:
+            side = self._side_streams[device] = torch.cuda.Stream(device=device)
+        side.wait_stream(main)
+        contexts: list[Any] = [None] * len(runs)
+        front_done: list[Any] = [None] * len(runs)
+
+        def front(i: int) -> None:
+            bucket, run = runs[i]
+            with torch.cuda.stream(side):
+                contexts[i] = open_run(bucket, run, self.param_groups[bucket.group_index], arena=f"overlap{i % 3}")
+                run_front(contexts[i])
+                front_done[i] = torch.cuda.Event()
+                front_done[i].record(side)
+
+        with torch.cuda.stream(side):
+            self._step_adamw_groups()
+        front(0)
+        for i in range(len(runs)):
+            if i + 1 < len(runs):
+                front(i + 1)
+            main.wait_event(front_done[i])
+            result = run_core(contexts[i])
+            core_done = torch.cuda.Event()
+            core_done.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(core_done)
+                apply_result(result, contexts[i].group)
+            contexts[i] = None
+        main.wait_stream(side)
 
     def _ensure_buckets(self) -> list[Bucket]:
         if self._buckets is None:
             self._buckets = build_buckets(self.param_groups, self.state)
         return self._buckets
 
-    def _step_bucket(self, bucket: Bucket) -> None:
-        """Step the bucket's parameters that have gradients, in runs of consecutive parameters.
+    def _runs_of(self, bucket: Bucket) -> list[list[int]]:
+        """The bucket's parameters that have gradients, as runs of consecutive positions.
 
         A run ends at a parameter without a gradient or when it would exceed
         ``MAX_RUN_ELEMENTS`` update elements (a larger parameter runs alone).
         """
-        group = self.param_groups[bucket.group_index]
+        runs: list[list[int]] = []
         pending: list[int] = []
         elements = 0
         for position, param in enumerate(bucket.params):
             size = run_elements(bucket, position)
             if pending and (param.grad is None or elements + size > MAX_RUN_ELEMENTS):
-                step_run(bucket, pending, group, self.state)
+                runs.append(pending)
                 pending, elements = [], 0
             if param.grad is not None:
                 pending.append(position)
                 elements += size
         if pending:
-            step_run(bucket, pending, group, self.state)
+            runs.append(pending)
+        return runs
+
+    def _step_bucket(self, bucket: Bucket) -> None:
+        """Step one bucket, run after run, on the current stream."""
+        group = self.param_groups[bucket.group_index]
+        for run in self._runs_of(bucket):
+            step_run(bucket, run, group, self.state)
 
 
 class Dion(IntegratedEMAOptimizer, _DionCore):
