@@ -270,6 +270,8 @@ def run_gpu_arm(args) -> None:
         optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
     else:
         optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+    if args.no_overlap:
+        optimizer.overlap_streams = False
     gen = torch.Generator(device=device).manual_seed(1)
     for p in model.parameters():
         p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
@@ -413,6 +415,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--config", choices=sorted(CONFIGS), default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

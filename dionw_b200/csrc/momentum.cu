@@ -1,6 +1,10 @@
 // HBM-bound passes over bucketed momentum: accumulate + row scores, row
 // selection, error-feedback decay + pack to the Newton-Schulz operand.
 //
+// Every byte these kernels touch is used once per step, so their loads and stores carry
+// the streaming (evict-first) hint: they run next to the tensor-core products on another
+// stream and must not push the products' operands out of L2.
+//
 // Row kernels give one warp to one row.  The row is walked in chunks of 1024
 // elements; lane t of the warp owns the float4 slots t, t+32, ..., t+224 of a
 // chunk, i.e. the "score lanes" 4(t+32q)+i of the documented 1024-lane order,
@@ -70,7 +74,7 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, boo
 
 __device__ __forceinline__ void load4f(const float* p, bool vec, long long e, long long cols, float (&out)[4]) {
   if (vec) {
-    const float4 v = *reinterpret_cast<const float4*>(p + e);
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(p + e));
     out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
   } else {
 #pragma unroll
@@ -80,7 +84,7 @@ __device__ __forceinline__ void load4f(const float* p, bool vec, long long e, lo
 
 __device__ __forceinline__ void store4f(float* p, bool vec, long long e, long long cols, const float (&v)[4]) {
   if (vec) {
-    *reinterpret_cast<float4*>(p + e) = make_float4(v[0], v[1], v[2], v[3]);
+    __stcs(reinterpret_cast<float4*>(p + e), make_float4(v[0], v[1], v[2], v[3]));
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -382,7 +386,7 @@ pack_rows_kernel(float* __restrict__ src, const int32_t* __restrict__ index, con
       uint2 packed;
       packed.x = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
       packed.y = uint32_t(h[2]) | (uint32_t(h[3]) << 16);
-      *reinterpret_cast<uint2*>(dst + e) = packed;
+      __stcs(reinterpret_cast<uint2*>(dst + e), packed);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i)

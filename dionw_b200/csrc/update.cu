@@ -23,7 +23,7 @@ row_sumsq_bf16_kernel(const uint16_t* __restrict__ o, long long total_rows, long
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (vec) {
     for (long long e = 8LL * lane; e < cols; e += 256) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(src + e);
+      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(src + e));
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -125,10 +125,10 @@ apply_run_kernel(const WeightTable tab, long long first_row, long long total_row
   if (pos < 0) {
     if (vec) {
       for (long long e = 4LL * lane; e < cols; e += 128) {
-        float4 v = *reinterpret_cast<float4*>(w + e);
+        float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
         v.x = __fmul_rn(v.x, decay_factor); v.y = __fmul_rn(v.y, decay_factor);
         v.z = __fmul_rn(v.z, decay_factor); v.w = __fmul_rn(v.w, decay_factor);
-        *reinterpret_cast<float4*>(w + e) = v;
+        __stcs(reinterpret_cast<float4*>(w + e), v);
       }
     } else {
       for (long long e = lane; e < cols; e += 32) w[e] = __fmul_rn(w[e], decay_factor);
@@ -140,8 +140,8 @@ apply_run_kernel(const WeightTable tab, long long first_row, long long total_row
   const float sc = scale[b];
   if (vec) {
     for (long long e = 4LL * lane; e < cols; e += 128) {
-      float4 v = *reinterpret_cast<float4*>(w + e);
-      const uint2 raw = *reinterpret_cast<const uint2*>(src + e);
+      float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
+      const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(src + e));
       float x[4] = {v.x, v.y, v.z, v.w};
       const float ov[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
                            __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
@@ -150,7 +150,7 @@ apply_run_kernel(const WeightTable tab, long long first_row, long long total_row
         if (has_decay) x[i] = __fmul_rn(x[i], decay_factor);
         x[i] = __fadd_rn(x[i], __fmul_rn(__fdiv_rn(ov[i], d), sc));
       }
-      *reinterpret_cast<float4*>(w + e) = make_float4(x[0], x[1], x[2], x[3]);
+      __stcs(reinterpret_cast<float4*>(w + e), make_float4(x[0], x[1], x[2], x[3]));
     }
   } else {
     for (long long e = lane; e < cols; e += 32) {
@@ -220,10 +220,10 @@ adamw_multi_kernel(const AdamTable tab, float lr, float beta1, float beta2, floa
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const long long e = base + 4LL * (threadIdx.x + j * kAdamThreads);
-      pv[j] = *reinterpret_cast<const float4*>(p + e);
+      pv[j] = __ldcs(reinterpret_cast<const float4*>(p + e));
       gv[j] = __ldcs(reinterpret_cast<const float4*>(g + e));
-      mv[j] = *reinterpret_cast<const float4*>(m + e);
-      vv[j] = *reinterpret_cast<const float4*>(v + e);
+      mv[j] = __ldcs(reinterpret_cast<const float4*>(m + e));
+      vv[j] = __ldcs(reinterpret_cast<const float4*>(v + e));
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -232,9 +232,9 @@ adamw_multi_kernel(const AdamTable tab, float lr, float beta1, float beta2, floa
       adamw_math(pv[j].y, gv[j].y, mv[j].y, vv[j].y, lr, beta1, beta2, weight_decay, eps, step_size, bc2_sqrt);
       adamw_math(pv[j].z, gv[j].z, mv[j].z, vv[j].z, lr, beta1, beta2, weight_decay, eps, step_size, bc2_sqrt);
       adamw_math(pv[j].w, gv[j].w, mv[j].w, vv[j].w, lr, beta1, beta2, weight_decay, eps, step_size, bc2_sqrt);
-      *reinterpret_cast<float4*>(p + e) = pv[j];
-      *reinterpret_cast<float4*>(m + e) = mv[j];
-      *reinterpret_cast<float4*>(v + e) = vv[j];
+      __stcs(reinterpret_cast<float4*>(p + e), pv[j]);
+      __stcs(reinterpret_cast<float4*>(m + e), mv[j]);
+      __stcs(reinterpret_cast<float4*>(v + e), vv[j]);
     }
   } else {
     const long long end = base + kAdamChunk < n ? base + kAdamChunk : n;
@@ -288,8 +288,8 @@ ema_multi_kernel(const EmaTable tab, float weight) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const long long e = base + 4LL * (threadIdx.x + j * kEmaThreads);
-      sv[j] = *reinterpret_cast<const float4*>(fsrc + e);
-      if (kOp == EmaOp::kLerp) dv[j] = *reinterpret_cast<const float4*>(dst + e);
+      sv[j] = __ldcs(reinterpret_cast<const float4*>(fsrc + e));
+      if (kOp == EmaOp::kLerp) dv[j] = __ldcs(reinterpret_cast<const float4*>(dst + e));
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -300,7 +300,7 @@ ema_multi_kernel(const EmaTable tab, float weight) {
       } else {
         dv[j] = sv[j];
       }
-      *reinterpret_cast<float4*>(dst + e) = dv[j];
+      __stcs(reinterpret_cast<float4*>(dst + e), dv[j]);
     }
   } else {
     const long long end = base + kEmaChunk < n ? base + kEmaChunk : n;

@@ -229,12 +229,16 @@ class _DionCore(Optimizer):
             if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
                 adamw_step(group, self.state)
 
-    # Two streams per step: the tensor-core part of run i (Newton-Schulz, on the
+    # Optional two-stream step: the tensor-core part of run i (Newton-Schulz, on the
     # caller's stream) overlaps the HBM-bound parts of its neighbours on a side
     # stream: accumulate/select/pack of run i+1, the weight update of run i-1,
     # and AdamW.  Three scratch arenas rotate.  The arithmetic and its order per
-    # run are unchanged, so results are bit-identical to the sequential step.
-    overlap_streams = True
+    # run are unchanged, so results are bit-identical to the one-stream step.
+    # Off by default: on a B200 under its 1 kW power cap the Llama-3-8B-shaped
+    # step takes the same 127.7 ms either way (SM clock 1230 MHz overlapped against
+    # 1365 MHz in sequence: the step is limited by power, not by idle units).  It
+    # pays where the step is not power-capped.
+    overlap_streams = False
 
     def _step_overlapped(self, runs: list[tuple[Bucket, list[int]]], device: torch.device) -> None:
         main = torch.cuda.current_stream(device)
