@@ -19,7 +19,7 @@ from torch import Tensor
 LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / "libdionw_b200.so"
 
 F32, F16, BF16 = 0, 1, 2
-NS_GRAM, NS_POLAR_EXPRESS, NS_KELLER = 0, 1, 2
+NS_GRAM, NS_POLAR_EXPRESS, NS_KELLER, NS_GRAM_FULL = 0, 1, 2, 3
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 _ERRORS = {
@@ -55,8 +55,8 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_newton_schulz_static": (
         c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p)),
     "dionw_symmetric_product": (
-        c_int, (c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float, c_float, c_void_p, c_int64,
-                c_void_p, c_float, c_int, c_void_p)),
+        c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_float, c_float,
+                c_void_p, c_int64, c_void_p, c_float, c_int, c_void_p)),
     "dionw_batched_gemm": (
         c_int, (c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int64, c_float, c_void_p, c_int64, c_int64,
                 c_int64, c_int64, c_int64, c_int, c_int, c_void_p)),
@@ -217,11 +217,12 @@ def newton_schulz_static(x: Tensor, out: Tensor, m: int, n: int, kind: int) -> N
                                                 kind, _stream(x)))
 
 
-def symmetric_product(a: Tensor, out: Tensor, *, cin: Tensor | None = None, alpha: float = 1.0,
-                      beta: float = 0.0, out2: Tensor | None = None, diag: float = 0.0) -> None:
+def symmetric_product(a: Tensor, out: Tensor, *, b: Tensor | None = None, cin: Tensor | None = None,
+                      alpha: float = 1.0, beta: float = 0.0, out2: Tensor | None = None, diag: float = 0.0) -> None:
     blocks, m, kdim = a.shape
     _check(library().dionw_symmetric_product(
-        a.data_ptr(), blocks, m, kdim, a.stride(-2), _ptr(cin), 0 if cin is None else cin.stride(-2), alpha, beta,
+        a.data_ptr(), _ptr(b), blocks, m, kdim, a.stride(-2), 0 if b is None else b.stride(-2), _ptr(cin),
+        0 if cin is None else cin.stride(-2), alpha, beta,
         out.data_ptr(), out.stride(-2), _ptr(out2), diag, dtype_code(a.dtype), _stream(a)))
 
 

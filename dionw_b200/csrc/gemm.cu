@@ -79,16 +79,24 @@ int host_sym_tiles(int tiles_m) {
 
 }  // namespace
 
-// C = alpha A A^T + beta Cin (lower tiles + mirror), optional second output with diag added.
-int symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, int64_t lda, int64_t a_batch,
-                      const void* cin, int64_t ldc, int64_t cin_batch, float alpha, float beta, void* out,
+// C = alpha A B^T + beta Cin for a product known to be symmetric (B = A, or A and B symmetric
+// matrices that commute): lower tiles + mirror, optional second output with diag added.
+// b == nullptr means B = A.
+int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, int64_t kdim, int64_t lda,
+                      int64_t a_batch, int64_t ldb, int64_t b_batch, const void* cin, int64_t ldc, int64_t cin_batch, float alpha, float beta, void* out,
                       int64_t ldo, int64_t out_batch, void* out2, float diag, int dtype, cudaStream_t stream) {
   DIONW_REQUIRE(dtype == DIONW_F16 || dtype == DIONW_BF16, "symmetric_product: dtype must be F16 or BF16");
   DIONW_REQUIRE(blocks > 0 && m > 0 && kdim > 0, "symmetric_product: empty problem");
   CUtensorMap map_a, map_b;
   int st = make_map(&map_a, a, dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBM);
   if (st != DIONW_OK) return st;
-  st = make_map(&map_b, a, dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBN);
+  const bool same = b == nullptr || b == a;
+  if (b == nullptr) {
+    b = a;
+    ldb = lda;
+    b_batch = a_batch;
+  }
+  st = make_map(&map_b, b, dtype, kdim, m, blocks, ldb, b_batch, gemm::kBK, gemm::kBN);
   if (st != DIONW_OK) return st;
   gemm::Params p{};
   p.cin = cin;
@@ -108,6 +116,7 @@ int symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, in
   p.tiles_m = int((m + gemm::kBM - 1) / gemm::kBM);
   p.tiles_n = int((m + gemm::kBN - 1) / gemm::kBN);
   p.tiles_per_batch = host_sym_tiles(p.tiles_m);
+  p.mirror_diagonal = same ? 0 : 1;
   p.status = device_status_word();
   if (dtype == DIONW_F16) return launch<__half, __half, false, true>(map_a, map_b, p, stream);
   return launch<__nv_bfloat16, __nv_bfloat16, false, true>(map_a, map_b, p, stream);
@@ -166,11 +175,12 @@ int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int
 
 }  // namespace dionw
 
-extern "C" int dionw_symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, int64_t lda,
-                                       const void* cin, int64_t ldc, float alpha, float beta, void* out,
-                                       int64_t ldo, void* out2, float diag, int dtype, void* stream) {
-  return dionw::symmetric_product(a, blocks, m, kdim, lda, m * lda, cin, ldc, m * ldc, alpha, beta, out, ldo,
-                                  m * ldo, out2, diag, dtype, static_cast<cudaStream_t>(stream));
+extern "C" int dionw_symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, int64_t kdim,
+                                       int64_t lda, int64_t ldb, const void* cin, int64_t ldc, float alpha,
+                                       float beta, void* out, int64_t ldo, void* out2, float diag, int dtype,
+                                       void* stream) {
+  return dionw::symmetric_product(a, b, blocks, m, kdim, lda, m * lda, ldb, m * ldb, cin, ldc, m * ldc, alpha, beta,
+                                  out, ldo, m * ldo, out2, diag, dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int b_is_nk,

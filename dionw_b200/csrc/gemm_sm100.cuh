@@ -33,7 +33,10 @@ constexpr uint32_t kABytes = kBM * kBK * 2;        // 16 KB
 constexpr uint32_t kBBytes = kBN * kBK * 2;        // 32 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kPanelBytes = 64 * kBK * 2;     // one 64-column panel of an MN-major B stage
-constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kMirrorPitch = 34;                   // halves per staged row: 17 words, conflict-free both ways
+constexpr uint32_t kMirrorBytes = 4 * 32 * kMirrorPitch * 2;  // one 32 x 32 staging tile per epilogue warp
+constexpr size_t kSmemBytes =
+    size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kMirrorBytes;
 
 constexpr int kWaitCode = 0x7001;
 
@@ -49,6 +52,7 @@ struct Params {
   int m, n, kdim;        // output m x n, reduction length kdim
   int batches;
   int tiles_m, tiles_n, tiles_per_batch;
+  int mirror_diagonal;   // symmetric schedule with B != A: also mirror inside the diagonal sub-blocks
   int* status;
 };
 
@@ -263,6 +267,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   uint64_t* acc_empty = acc_full + 2;         // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint16_t* mirror_stage = reinterpret_cast<uint16_t*>(smem + size_t(kStages) * kStageBytes + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -383,8 +388,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         uint32_t v[32];
         const uint32_t taddr = tmem_base + (uint32_t(sub * 32) << 16) + acc * uint32_t(kBN) + uint32_t(chunk * 32);
         tmem_load32(taddr, v);
-        if (!row_ok) continue;
         const bool full = (col0 + 32 <= p.n);
+        if constexpr (kSym) {
+          // Fast path for a strictly-lower 32 x 32 piece that lies wholly inside the matrix:
+          // rows are stored as they are, and the piece is turned through shared memory so
+          // that its transposed copy also leaves as 16-byte stores.
+          const int row0 = tile.tm * kBM + sub * 32;
+          if (side == 1 && full && row0 + 32 <= p.m && (p.ldo & 7) == 0 && (p.ldc & 7) == 0 &&
+              (reinterpret_cast<uintptr_t>(out_b) & 15u) == 0 &&
+              (out2_b == nullptr || (reinterpret_cast<uintptr_t>(out2_b) & 15u) == 0) &&
+              (cin_row == nullptr || (reinterpret_cast<uintptr_t>(cin_row) & 15u) == 0)) {
+            __align__(16) OutT r[32];
+            if (cin_row != nullptr) {
+              __align__(16) InT c[32];
+              const uint4* s4 = reinterpret_cast<const uint4*>(cin_row + col0);
+              uint4* c4 = reinterpret_cast<uint4*>(c);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) c4[j] = s4[j];
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                r[j] = from_float<OutT>(fmaf(p.beta, to_float<InT>(c[j]), p.alpha * __uint_as_float(v[j])));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
+            }
+            const uint4* s4 = reinterpret_cast<const uint4*>(r);
+            uint4* d4 = reinterpret_cast<uint4*>(out_b + size_t(row) * p.ldo + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) d4[j] = s4[j];
+            if (out2_b != nullptr) {
+              uint4* e4 = reinterpret_cast<uint4*>(out2_b + size_t(row) * p.ldo + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) e4[j] = s4[j];
+            }
+            uint16_t* stage = mirror_stage + sub * 32 * kMirrorPitch;
+            const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
+            uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) my_row[j] = words[j];
+            __syncwarp();
+            const int seg = lane & 3;  // which 8 of the 32 source rows this lane gathers
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int c = (lane >> 2) + 8 * it;  // source column = destination row
+              __align__(16) uint16_t gathered[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) gathered[q] = stage[(seg * 8 + q) * kMirrorPitch + c];
+              const size_t at = size_t(col0 + c) * p.ldo + row0 + seg * 8;
+              *reinterpret_cast<uint4*>(out_b + at) = *reinterpret_cast<const uint4*>(gathered);
+              if (out2_b != nullptr) *reinterpret_cast<uint4*>(out2_b + at) = *reinterpret_cast<const uint4*>(gathered);
+            }
+            __syncwarp();
+            continue;
+          }
+        }
+        if (!row_ok) continue;
         __align__(16) InT c[32];
         if (cin_row != nullptr) {
           const InT* src = cin_row + col0;
@@ -410,6 +468,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         OutT* dst = out_b + size_t(row) * p.ldo + col0;
+        if (kSym && side == 0 && p.mirror_diagonal != 0) {
+          // A B^T with B != A is symmetric only up to rounding: keep the lower triangle of
+          // the diagonal sub-block and mirror it, so that the stored matrix is exactly symmetric.
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col > row || col >= p.n) continue;
+            dst[j] = r[j];
+            if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col] = r2[j];
+            if (col < row) {
+              out_b[size_t(col) * p.ldo + row] = r[j];
+              if (out2_b != nullptr) out2_b[size_t(col) * p.ldo + row] = r[j];
+            }
+          }
+          continue;
+        }
         if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
           uint4* d4 = reinterpret_cast<uint4*>(dst);
           const uint4* s4 = reinterpret_cast<const uint4*>(r);
@@ -433,9 +506,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
           }
           if (side == 1) {
-            // Transposed copy: lanes hold consecutive rows, so each store
-            // instruction writes 32 consecutive elements of one output row.
-#pragma unroll
+            // Transposed copy of a strictly-lower sub-block (lanes hold consecutive rows).
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < p.n) {
                 out_b[size_t(col0 + j) * p.ldo + row] = r[j];

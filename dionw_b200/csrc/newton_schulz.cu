@@ -4,8 +4,8 @@
 
 namespace dionw {
 
-int symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim, int64_t lda, int64_t a_batch,
-                      const void* cin, int64_t ldc, int64_t cin_batch, float alpha, float beta, void* out,
+int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, int64_t kdim, int64_t lda,
+                      int64_t a_batch, int64_t ldb, int64_t b_batch, const void* cin, int64_t ldc, int64_t cin_batch, float alpha, float beta, void* out,
                       int64_t ldo, int64_t out_batch, void* out2, float diag, int dtype, cudaStream_t stream);
 int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int64_t ldb, int64_t b_batch,
                  bool b_is_nk, const void* cin, int64_t ldc, int64_t cin_batch, float beta, void* out, int64_t ldo,
@@ -56,7 +56,7 @@ Layout layout_of(int64_t blocks, int64_t m, int64_t n, int64_t ldx, int kind) {
   l.ldg = round_up(m, 8);
   l.x_bytes = align256(size_t(blocks) * m * ldx * 2);
   l.g_bytes = align256(size_t(blocks) * m * l.ldg * 2);
-  l.wide_gram = (kind == DIONW_NS_GRAM) && n > m;
+  l.wide_gram = (kind == DIONW_NS_GRAM || kind == DIONW_NS_GRAM_FULL) && n > m;
   return l;
 }
 
@@ -80,7 +80,8 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
                                    void* workspace, size_t workspace_bytes, void* stream_ptr) {
   using namespace dionw;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  DIONW_REQUIRE(kind == DIONW_NS_GRAM || kind == DIONW_NS_POLAR_EXPRESS || kind == DIONW_NS_KELLER,
+  DIONW_REQUIRE(kind == DIONW_NS_GRAM || kind == DIONW_NS_POLAR_EXPRESS || kind == DIONW_NS_KELLER ||
+                    kind == DIONW_NS_GRAM_FULL,
                 "newton_schulz: unknown kind %d", kind);
   DIONW_REQUIRE(blocks > 0 && m > 0 && n >= m, "newton_schulz: needs blocks > 0 and 0 < m <= n (got %lld, %lld, %lld)",
                 (long long)blocks, (long long)m, (long long)n);
@@ -94,7 +95,12 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
               bytes_of(l) + lost);
     return DIONW_ERR_WORKSPACE;
   }
-  const int dt = kind == DIONW_NS_GRAM ? DIONW_F16 : DIONW_BF16;
+  const bool gram = kind == DIONW_NS_GRAM || kind == DIONW_NS_GRAM_FULL;
+  const int dt = gram ? DIONW_F16 : DIONW_BF16;
+  // Every m x m matrix of the Gram schedule is a polynomial in one symmetric G, so the
+  // products among them are symmetric too: GRAM computes their lower tiles and mirrors,
+  // GRAM_FULL computes them as general products, as the reference's cuBLAS calls do.
+  const bool mirror = kind == DIONW_NS_GRAM;
   const int64_t xb = m * ldx;       // batch strides in elements
   const int64_t gb = m * l.ldg;
   const int64_t ldg = l.ldg;
@@ -117,7 +123,7 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
     void* q = q0;
     void* qnext = q1;
     // G = X X^T
-    DIONW_STEP(symmetric_product(xcur, blocks, m, n, ldx, xb, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb, nullptr, 0.0f,
+    DIONW_STEP(symmetric_product(xcur, nullptr, blocks, m, n, ldx, xb, 0, 0, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb, nullptr, 0.0f,
                                  dt, stream));
     for (int i = 0; i < 5; ++i) {
       const Coeff k = kGram[i];
@@ -126,27 +132,38 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
         DIONW_STEP(batched_gemm(q, ldg, gb, xcur, ldx, xb, false, nullptr, 0, 0, 0.0f, x1, ldx, xb, blocks, m, n, m,
                                 dt, dt, stream));
         xcur = x1;
-        DIONW_STEP(symmetric_product(xcur, blocks, m, n, ldx, xb, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb, nullptr,
-                                     0.0f, dt, stream));
+        DIONW_STEP(symmetric_product(xcur, nullptr, blocks, m, n, ldx, xb, 0, 0, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb,
+                                     nullptr, 0.0f, dt, stream));
       }
       const bool fresh_q = (i == 0 || i == kRestart);
       // Z = c G G^T + b G; on a fresh start also Q = Z + a I
-      DIONW_STEP(symmetric_product(g, blocks, m, m, ldg, gb, g, ldg, gb, float(k.c), float(k.b), z, ldg, gb,
+      DIONW_STEP(symmetric_product(g, nullptr, blocks, m, m, ldg, gb, 0, 0, g, ldg, gb, float(k.c), float(k.b), z, ldg, gb,
                                    fresh_q ? q : nullptr, half_round(k.a), dt, stream));
       if (!fresh_q) {
         // Q <- a Q + Q Z   (Z is stored symmetric, so Z^T == Z bit for bit)
-        DIONW_STEP(batched_gemm(q, ldg, gb, z, ldg, gb, true, q, ldg, gb, float(k.a), qnext, ldg, gb, blocks, m, m,
-                                m, dt, dt, stream));
+        if (mirror)
+          DIONW_STEP(symmetric_product(q, z, blocks, m, m, ldg, gb, ldg, gb, q, ldg, gb, 1.0f, float(k.a), qnext, ldg,
+                                       gb, nullptr, 0.0f, dt, stream));
+        else
+          DIONW_STEP(batched_gemm(q, ldg, gb, z, ldg, gb, true, q, ldg, gb, float(k.a), qnext, ldg, gb, blocks, m,
+                                  m, m, dt, dt, stream));
         void* t = q;
         q = qnext;
         qnext = t;
       }
       if (i < 4 && i + 1 != kRestart) {
         // RZ = a G + G Z ; G <- a RZ + Z RZ
-        DIONW_STEP(batched_gemm(g, ldg, gb, z, ldg, gb, true, g, ldg, gb, float(k.a), rz, ldg, gb, blocks, m, m, m,
-                                dt, dt, stream));
-        DIONW_STEP(batched_gemm(z, ldg, gb, rz, ldg, gb, false, rz, ldg, gb, float(k.a), g, ldg, gb, blocks, m, m,
-                                m, dt, dt, stream));
+        if (mirror) {
+          DIONW_STEP(symmetric_product(g, z, blocks, m, m, ldg, gb, ldg, gb, g, ldg, gb, 1.0f, float(k.a), rz, ldg,
+                                       gb, nullptr, 0.0f, dt, stream));
+          DIONW_STEP(symmetric_product(z, rz, blocks, m, m, ldg, gb, ldg, gb, rz, ldg, gb, 1.0f, float(k.a), g, ldg,
+                                       gb, nullptr, 0.0f, dt, stream));
+        } else {
+          DIONW_STEP(batched_gemm(g, ldg, gb, z, ldg, gb, true, g, ldg, gb, float(k.a), rz, ldg, gb, blocks, m, m,
+                                  m, dt, dt, stream));
+          DIONW_STEP(batched_gemm(z, ldg, gb, rz, ldg, gb, false, rz, ldg, gb, float(k.a), g, ldg, gb, blocks, m,
+                                  m, m, dt, dt, stream));
+        }
       }
     }
     // out = Q X in bf16
@@ -156,7 +173,7 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
   }
 
   // Standard iteration: X <- a X + (b G + c G^2) X with G = X X^T.
-  const Coeff* table = kind == DIONW_NS_GRAM ? kGram : (kind == DIONW_NS_POLAR_EXPRESS ? kPolarExpress : kKeller);
+  const Coeff* table = gram ? kGram : (kind == DIONW_NS_POLAR_EXPRESS ? kPolarExpress : kKeller);
   void* x1 = ws;
   void* x2 = ws + l.x_bytes;
   void* g = ws + 2 * l.x_bytes;
@@ -165,9 +182,9 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
   for (int i = 0; i < 5; ++i) {
     const Coeff k = table[i];
     void* next = (i == 4) ? out : ((cur == x1) ? x2 : x1);
-    DIONW_STEP(symmetric_product(cur, blocks, m, n, ldx, xb, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb, nullptr, 0.0f,
+    DIONW_STEP(symmetric_product(cur, nullptr, blocks, m, n, ldx, xb, 0, 0, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb, nullptr, 0.0f,
                                  dt, stream));
-    DIONW_STEP(symmetric_product(g, blocks, m, m, ldg, gb, g, ldg, gb, float(k.c), float(k.b), poly, ldg, gb,
+    DIONW_STEP(symmetric_product(g, nullptr, blocks, m, m, ldg, gb, 0, 0, g, ldg, gb, float(k.c), float(k.b), poly, ldg, gb,
                                  nullptr, 0.0f, dt, stream));
     DIONW_STEP(batched_gemm(poly, ldg, gb, cur, ldx, xb, false, cur, ldx, xb, float(k.a), next, ldx, xb, blocks, m,
                             n, m, dt, i == 4 ? DIONW_BF16 : dt, stream));

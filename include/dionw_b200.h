@@ -42,6 +42,9 @@ extern "C" {
 #define DIONW_NS_GRAM 0
 #define DIONW_NS_POLAR_EXPRESS 1
 #define DIONW_NS_KELLER 2
+/* GRAM with the products among symmetric matrices computed in full, as the
+ * reference's cuBLAS calls do, instead of on one triangle of tiles. */
+#define DIONW_NS_GRAM_FULL 3
 
 /* Text of the last error on the calling thread (copied, NUL-terminated). */
 void dionw_last_error(char* buffer, size_t size);
@@ -113,8 +116,9 @@ size_t dionw_newton_schulz_workspace_bytes(int64_t blocks, int64_t m, int64_t n,
 /* Five quintic steps on wide or square [blocks, m, ldx] operands (m <= n),
  * already normalised and rounded to fp16 (GRAM) or bf16 (the other kinds);
  * x is overwritten; out receives bf16 [blocks, m, ldx].  out may alias x.
- * GRAM follows gram_polar_express / _gram / _standard (src/dionw/_gram.py:41-89)
- * product by product, with the symmetric products (ns_line_1, ns_line_2,
+ * GRAM and GRAM_FULL follow gram_polar_express / _gram / _standard
+ * (src/dionw/_gram.py:41-89) product by product (GRAM mirrors the m x m products
+ * that are symmetric, GRAM_FULL computes them in full), with the symmetric products (ns_line_1, ns_line_2,
  * src/dionw/_symmetric_kernels.py:252-312) computed on one triangle of tiles
  * by tcgen05 tensor-core kernels fed by TMA.  POLAR_EXPRESS / KELLER follow
  * quintic_triton (src/dionw/_polar_express.py:74-104, src/dionw/_keller.py). */
@@ -141,15 +145,18 @@ int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m, int64_t n
 int dionw_newton_schulz_static(void* x, void* out, int64_t blocks, int64_t m, int64_t n,
                                int64_t ldx, int kind, void* stream);
 
-/* C = alpha * A A^T + beta * Cin on the lower triangle of tiles, mirrored;
- * out2 (optional) = C + diag * I.  A is [blocks, m, lda] with kdim columns.
- * dtype F16 or BF16 for every operand.  ns_line_1 is alpha=1, beta=0, cin=NULL;
- * ns_line_2 is A = Cin = the symmetric input
- * (src/dionw/_symmetric_kernels.py:252-312). */
-int dionw_symmetric_product(const void* a, int64_t blocks, int64_t m, int64_t kdim,
-                            int64_t lda, const void* cin, int64_t ldc, float alpha,
-                            float beta, void* out, int64_t ldo, void* out2, float diag,
-                            int dtype, void* stream);
+/* C = alpha * A B^T + beta * Cin for a product that is symmetric: computed on
+ * the lower triangle of tiles and mirrored, so C is exactly symmetric; out2
+ * (optional) = C + diag * I.  A and B are [blocks, m, ld] with kdim columns;
+ * b == NULL means B = A.  dtype F16 or BF16 for every operand.  ns_line_1 is
+ * b=NULL, alpha=1, beta=0, cin=NULL; ns_line_2 is A = Cin = the symmetric input
+ * (src/dionw/_symmetric_kernels.py:252-312).  With B != A the caller asserts
+ * that A B^T is symmetric (both symmetric and commuting, as the polynomials of
+ * one Gram matrix at src/dionw/_gram.py:64-68 are). */
+int dionw_symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m,
+                            int64_t kdim, int64_t lda, int64_t ldb, const void* cin,
+                            int64_t ldc, float alpha, float beta, void* out, int64_t ldo,
+                            void* out2, float diag, int dtype, void* stream);
 
 /* C = A B + beta * Cin, A [blocks, m, lda] (m x kdim).  b_is_nk = 0: B is
  * [blocks, kdim, ldb] row-major (kdim x n); b_is_nk = 1: B is given as

@@ -179,6 +179,27 @@ def test_symmetric_product_polynomial_and_identity(native, m) -> None:
     assert torch.equal(out, out.mT)
 
 
+@pytest.mark.parametrize("m", [256, 520])
+def test_symmetric_product_of_two_commuting_matrices(native, m) -> None:
+    """``a Q + Q Z`` for polynomials Q, Z of one symmetric matrix (src/dionw/_gram.py:64-68):
+    the lower triangle equals the general product, the upper one is its mirror."""
+    base = torch.randn(2, m, m, generator=_gen(15)) / math.sqrt(m)
+    g = base @ base.mT
+    q = (0.3 * g + 0.5 * g @ g).half().to(DEV)
+    z = (1.1 * g - 0.2 * g @ g @ g).half().to(DEV)
+    q = torch.tril(q) + torch.tril(q, -1).mT
+    z = torch.tril(z) + torch.tril(z, -1).mT
+    out = torch.empty_like(q)
+    native.symmetric_product(q, out, b=z, cin=q, alpha=1.0, beta=0.7)
+    assert native.device_status() == 0
+    general = torch.empty_like(q)
+    native.batched_gemm(q, z, general, b_is_nk=True, cin=q, beta=0.7)
+    assert torch.equal(torch.tril(out), torch.tril(general))
+    assert torch.equal(out, out.mT)
+    expect = (q.float() @ z.float() + 0.7 * q.float()).half()
+    assert rel_l2(out.float(), expect.float()) < 2e-3
+
+
 @pytest.mark.parametrize("b_is_nk", [True, False])
 @pytest.mark.parametrize("blocks,m,n,kdim", [(2, 64, 256, 64), (1, 300, 520, 200), (2, 256, 1024, 256), (1, 128, 4096, 1024)])
 def test_batched_gemm(native, b_is_nk, blocks, m, n, kdim) -> None:
@@ -208,8 +229,8 @@ def _run_ns(native, x32: torch.Tensor, kind: int) -> torch.Tensor:
     wide = x32.mT.contiguous() if tall else x32
     m, n = wide.shape[1:]
     ld = (n + 7) // 8 * 8
-    dtype = torch.float16 if kind == 0 else torch.bfloat16
-    if kind == 0:
+    dtype = torch.float16 if kind in (0, 3) else torch.bfloat16
+    if kind in (0, 3):
         xn = (wide / (torch.linalg.vector_norm(wide, dim=(-2, -1), keepdim=True) + 1e-8)).to(dtype)
     else:
         safety = 1.02 if kind == 1 else 1.0
@@ -252,6 +273,23 @@ def test_gram_newton_schulz_matches_oracle(native, blocks, m, n) -> None:
     eye = torch.eye(m, dtype=torch.float64)
     ref_gram = expect.double() @ expect.double().mT
     assert float((gram - eye).norm()) < 1.2 * float((ref_gram - eye).norm()) + 0.05
+
+
+@pytest.mark.parametrize("blocks,m,n", [(2, 512, 2048), (1, 1024, 1280)])
+def test_mirrored_gram_products_stay_within_the_rounding_of_the_full_ones(native, blocks, m, n) -> None:
+    """GRAM mirrors ``aQ + QZ``, ``aG + GZ`` and ``aRZ + Z RZ`` (symmetric in exact arithmetic);
+    GRAM_FULL computes them in full like the reference.  Both must sit at the same distance from
+    the rounding-free polynomial and from an orthogonal matrix."""
+    x = torch.randn(blocks, m, n, generator=_gen(16))
+    mirrored = _run_ns(native, x, 0).float()
+    full = _run_ns(native, x, 3).float()
+    assert rel_l2(mirrored, full) < 1e-2  # nearly square operands amplify fp16 rounding either way
+    target = oracle.polynomial_fp64(x, eps=1e-8)
+    assert rel_l2(mirrored, target) < 1.3 * rel_l2(full, target) + 3e-3
+    eye = torch.eye(m, dtype=torch.float64)
+    err_m = float((mirrored.double() @ mirrored.double().mT - eye).norm())
+    err_f = float((full.double() @ full.double().mT - eye).norm())
+    assert err_m < 1.2 * err_f + 0.05
 
 
 @pytest.mark.parametrize("kind,name", [(1, "polar_express_triton"), (2, "keller_triton")])
