@@ -237,17 +237,31 @@ class ShardedDion(_DionCore):
     def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
         return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
 
+    # Update elements one round may hold per rank.  Smaller rounds give the weight update of
+    # round t (an HBM-bound pass over every replica, on a side stream) a Newton-Schulz of round
+    # t+1 to hide behind; the single-GPU cap bounds it from above.
+    round_elements = 1 << 26
+
     def _step_matrices(self) -> None:
         import dionw_b200.optimizer as optimizer_module  # MAX_RUN_ELEMENTS is looked up at call time
 
-        limit = optimizer_module.MAX_RUN_ELEMENTS
+        limit = min(optimizer_module.MAX_RUN_ELEMENTS, self.round_elements)
         world, me = self._world, self._rank
+        shared = self._ensure_shared()
+        if not shared:
+            return
+        device = shared[0].params[0].device
+        main = torch.cuda.current_stream(device)
+        side = self._side_streams.get(device)
+        if side is None:
+            side = self._side_streams[device] = torch.cuda.Stream(device=device)
+        side.wait_stream(main)
         pending: _Round | None = None
+        applied: list[Any] = []  # applied[t]: event recorded on the side stream after round t's update
         round_id = 0
-        for sb in self._ensure_shared():
+        for sb in shared:
             group = self.param_groups[sb.group_index]
             selecting = sb.k < sb.rows
-            device = sb.params[0].device
             per_rank = [[i for i, o in enumerate(sb.owners) if o == r] for r in range(world)]
             runs = []
             for members in per_rank:
@@ -258,6 +272,9 @@ class ShardedDion(_DionCore):
                 counts = [sum(sb.blocks[i] for i in c) for c in chosen]
                 slot = max(_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, selecting))[1]
                            if c else 0 for c in counts)
+                if round_id >= 2:
+                    # This round reuses the send and receive arenas of round_id - 2.
+                    main.wait_event(applied[round_id - 2])
                 name = f"run{round_id % 2}"
                 _workspace.arena(device, slot, name)
                 if chosen[me]:
@@ -273,27 +290,36 @@ class ShardedDion(_DionCore):
                 issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
                                 [[sb.blocks[i] for i in c] for c in chosen], sb, group)
                 if pending is not None:
-                    self._apply_round(pending)
+                    applied.append(self._apply_round(pending, main, side))
                 pending = issued
                 round_id += 1
         if pending is not None:
-            self._apply_round(pending)
+            applied.append(self._apply_round(pending, main, side))
+        main.wait_stream(side)
 
-    def _apply_round(self, rnd: _Round) -> None:
-        if rnd.work is not None:
-            rnd.work.wait()
-        sb = rnd.bucket
-        selecting = sb.k < sb.rows
-        for rank, count in enumerate(rnd.counts):
-            if count == 0:
-                continue
-            got = _workspace.views(rnd.recv, _matrix_step.exchange_plan(count, sb.rows, sb.k, sb.cols, selecting),
-                                   base=rank * rnd.slot)
-            result = _matrix_step.RunResult(
-                params=rnd.params[rank], rows_per_tensor=[b * sb.rows for b in rnd.blocks[rank]], count=count,
-                rows=sb.rows, k=sb.k, cols=sb.cols, orthogonal=got["x"], rowmap=got.get("rowmap"),
-                denom=got["denom"], scale=got["scale"])
-            _matrix_step.apply_result(result, rnd.group)
+    def _apply_round(self, rnd: _Round, main: Any, side: Any) -> Any:
+        """Every rank's contribution of one round applied to this replica, on the side stream."""
+        with torch.cuda.stream(side):
+            if rnd.work is not None:
+                rnd.work.wait()          # the side stream waits for the gather
+            else:
+                side.wait_stream(main)   # one rank: the "received" data is the local result
+            sb = rnd.bucket
+            selecting = sb.k < sb.rows
+            for rank, count in enumerate(rnd.counts):
+                if count == 0:
+                    continue
+                got = _workspace.views(rnd.recv,
+                                       _matrix_step.exchange_plan(count, sb.rows, sb.k, sb.cols, selecting),
+                                       base=rank * rnd.slot)
+                result = _matrix_step.RunResult(
+                    params=rnd.params[rank], rows_per_tensor=[b * sb.rows for b in rnd.blocks[rank]], count=count,
+                    rows=sb.rows, k=sb.k, cols=sb.cols, orthogonal=got["x"], rowmap=got.get("rowmap"),
+                    denom=got["denom"], scale=got["scale"])
+                _matrix_step.apply_result(result, rnd.group)
+            done = torch.cuda.Event()
+            done.record(side)
+        return done
 
     def _step_adamw(self) -> list[Any]:
         gathers: list[Any] = []
