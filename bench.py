@@ -268,6 +268,10 @@ def run_gpu_arm(args) -> None:
         from dionw_b200.distributed import ShardedDion
 
         optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+        if args.no_overlap:
+            optimizer.overlap_apply = False
+        if args.round_elements:
+            optimizer.round_elements = args.round_elements
     else:
         optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
     if args.no_overlap:
@@ -416,6 +420,7 @@ def main() -> None:
     parser.add_argument("--config", choices=sorted(CONFIGS), default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -237,10 +237,14 @@ class ShardedDion(_DionCore):
     def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
         return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
 
-    # Update elements one round may hold per rank.  Smaller rounds give the weight update of
-    # round t (an HBM-bound pass over every replica, on a side stream) a Newton-Schulz of round
-    # t+1 to hide behind; the single-GPU cap bounds it from above.
-    round_elements = 1 << 26
+    # Update elements one round may hold per rank (the single-GPU cap bounds it from above),
+    # and whether the weight update of round t runs on a side stream next to the Newton-Schulz
+    # of round t+1.  Measured on 2 x B200 with the Llama-3-8B shapes: in line with full-size
+    # rounds 60.4 ms/step; in line with 2^26-element rounds 63.2; overlapped 64.8 (2^26) and
+    # 68.7 (2^25) -- the streaming update slows the tensor-core products it runs beside by more
+    # than it hides, so both stay off.
+    round_elements = 1 << 28
+    overlap_apply = False
 
     def _step_matrices(self) -> None:
         import dionw_b200.optimizer as optimizer_module  # MAX_RUN_ELEMENTS is looked up at call time
@@ -255,7 +259,10 @@ class ShardedDion(_DionCore):
         side = self._side_streams.get(device)
         if side is None:
             side = self._side_streams[device] = torch.cuda.Stream(device=device)
-        side.wait_stream(main)
+        if not self.overlap_apply:
+            side = main
+        else:
+            side.wait_stream(main)
         pending: _Round | None = None
         applied: list[Any] = []  # applied[t]: event recorded on the side stream after round t's update
         round_id = 0
@@ -295,14 +302,15 @@ class ShardedDion(_DionCore):
                 round_id += 1
         if pending is not None:
             applied.append(self._apply_round(pending, main, side))
-        main.wait_stream(side)
+        if side is not main:
+            main.wait_stream(side)
 
     def _apply_round(self, rnd: _Round, main: Any, side: Any) -> Any:
         """Every rank's contribution of one round applied to this replica, on the side stream."""
         with torch.cuda.stream(side):
             if rnd.work is not None:
                 rnd.work.wait()          # the side stream waits for the gather
-            else:
+            elif side is not main:
                 side.wait_stream(main)   # one rank: the "received" data is the local result
             sb = rnd.bucket
             selecting = sb.k < sb.rows
