@@ -1,6 +1,6 @@
 // Batched tcgen05 GEMM for sm_100a: TMA-fed shared-memory ring, accumulators in
 // TMEM, a persistent tile loop with three warp roles (TMA producer, MMA issuer,
-// four epilogue warps).  Two tile schedules: every tile of a general product,
+// eight epilogue warps).  Two tile schedules: every tile of a general product,
 // or only the tiles on and below the diagonal of a symmetric product, whose
 // strictly-lower 128x128 sub-blocks are also stored transposed.
 //
@@ -26,15 +26,15 @@ constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kABytes = kBM * kBK * 2;        // 16 KB
 constexpr uint32_t kBBytes = kBN * kBK * 2;        // 32 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kPanelBytes = 64 * kBK * 2;     // one 64-column panel of an MN-major B stage
 constexpr int kMirrorPitch = 34;                   // halves per staged row: 17 words, conflict-free both ways
-constexpr uint32_t kMirrorBytes = 4 * 32 * kMirrorPitch * 2;  // one 32 x 32 staging tile per epilogue warp
+constexpr uint32_t kMirrorBytes = 8 * 32 * kMirrorPitch * 2;  // one 32 x 32 staging tile per epilogue warp
 constexpr size_t kSmemBytes =
     size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kMirrorBytes;
 
@@ -356,121 +356,160 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    // Eight warps: two per TMEM sub-partition (a warp may only read the 32 lanes
+    // 32 * (warp % 4) ...), each taking four of the tile's eight 32-column chunks.
+    const int ew = warp - 2;                  // 0..7
     const int sub = warp & 3;                 // TMEM lanes 32*sub .. 32*sub+31
+    const int first_chunk = (ew >> 2) * (kBN / 64);
     const int row_in_tile = sub * 32 + lane;
     const InT* cin = reinterpret_cast<const InT*>(p.cin);
     OutT* out = reinterpret_cast<OutT*>(p.out);
     OutT* out2 = reinterpret_cast<OutT*>(p.out2);
+    uint16_t* stage = mirror_stage + ew * 32 * kMirrorPitch;
     uint32_t local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
       const Tile tile = kSym ? sym_tile(t, p) : general_tile(t, p);
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status)) { ok = false; break; }
-      tc_fence_after();
       const int row = tile.tm * kBM + row_in_tile;
+      const int row0 = tile.tm * kBM + sub * 32;
       const bool row_ok = row < p.m;
       const InT* cin_row = cin ? cin + size_t(tile.batch) * p.cin_batch + size_t(row) * p.ldc : nullptr;
       OutT* out_b = out + size_t(tile.batch) * p.out_batch;
       OutT* out2_b = out2 ? out2 + size_t(tile.batch) * p.out_batch : nullptr;
-#pragma unroll 1
-      for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+      // Class of the 32 x 32 piece at (row0, col0) under the symmetric schedule:
+      // 0 stored as it is; 1 strictly below the diagonal: stored and stored transposed;
+      // 2 strictly above: skipped (its mirror image writes it); 3 on the diagonal of a
+      // product with B != A: lower triangle stored and mirrored element by element.
+      auto class_of = [&](int col0) -> int {
+        if constexpr (!kSym) return 0;
+        if (col0 + 32 <= row0) return 1;
+        if (col0 >= row0 + 32) return 2;
+        return p.mirror_diagonal != 0 ? 3 : 0;
+      };
+      // Pieces wholly inside the matrix move between global memory and registers in
+      // "piece order": lane l holds 8 consecutive elements of row 8*it + l/4 at column
+      // 8*(l%4), it = 0..3, so one instruction touches 8 rows x 64 contiguous bytes.  The
+      // accumulator arrives in "row order" (lane = row); a 32 x 34 staging tile in shared
+      // memory converts between the two.
+      const bool aligned = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out_b) & 15u) == 0 &&
+                           (out2_b == nullptr || (reinterpret_cast<uintptr_t>(out2_b) & 15u) == 0) &&
+                           (cin == nullptr || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(cin) & 15u) == 0 &&
+                                               (p.cin_batch & 7) == 0));
+      const bool rows_inside = row0 + 32 <= p.m;
+      const int piece_row = lane >> 2, piece_col = (lane & 3) * 8;
+      auto fast_piece = [&](int col0, int cls) { return aligned && rows_inside && col0 + 32 <= p.n && cls != 3; };
+      // The epilogue is a chain of dependent latencies; the Cin piece of the next chunk is
+      // requested before the current chunk is worked on.  (Requesting all four chunks of a
+      // tile up front was measured slower: 48 more live registers for no shorter chain.)
+      uint4 ahead[4];
+      auto prefetch = [&](int chunk) {
         const int col0 = tile.tn * kBN + chunk * 32;
-        // Which side of the diagonal this 128-column sub-block lies on.
-        int side = 0;  // 0: ordinary store; 1: also store transposed; 2: skip
-        if constexpr (kSym) {
-          const int col_block = col0 / kBM;
-          side = col_block < tile.tm ? 1 : (col_block == tile.tm ? 0 : 2);
-        }
-        if (col0 >= p.n) break;        // uniform over the warp
-        if (side == 2) continue;       // uniform over the warp
+        const int cls = class_of(col0);
+        if (cin == nullptr || cls == 2 || !fast_piece(col0, cls)) return;
+        const InT* base = cin + size_t(tile.batch) * p.cin_batch + size_t(row0 + piece_row) * p.ldc + col0 + piece_col;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) ahead[it] = *reinterpret_cast<const uint4*>(base + size_t(8 * it) * p.ldc);
+      };
+      prefetch(first_chunk);   // does not depend on the accumulator: overlaps the wait below
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
+#pragma unroll 1
+      for (int chunk = first_chunk; chunk < first_chunk + kBN / 64; ++chunk) {
+        const int col0 = tile.tn * kBN + chunk * 32;
+        const int cls = class_of(col0);
+        uint4 now[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) now[j] = ahead[j];
+        if (chunk + 1 < first_chunk + kBN / 64) prefetch(chunk + 1);
+        if (col0 >= p.n) break;       // uniform over the warp
+        if (cls == 2) continue;       // uniform over the warp
         uint32_t v[32];
         const uint32_t taddr = tmem_base + (uint32_t(sub * 32) << 16) + acc * uint32_t(kBN) + uint32_t(chunk * 32);
         tmem_load32(taddr, v);
-        const bool full = (col0 + 32 <= p.n);
-        if constexpr (kSym) {
-          // Fast path for a strictly-lower 32 x 32 piece that lies wholly inside the matrix:
-          // rows are stored as they are, and the piece is turned through shared memory so
-          // that its transposed copy also leaves as 16-byte stores.
-          const int row0 = tile.tm * kBM + sub * 32;
-          if (side == 1 && full && row0 + 32 <= p.m && (p.ldo & 7) == 0 && (p.ldc & 7) == 0 &&
-              (reinterpret_cast<uintptr_t>(out_b) & 15u) == 0 &&
-              (out2_b == nullptr || (reinterpret_cast<uintptr_t>(out2_b) & 15u) == 0) &&
-              (cin_row == nullptr || (reinterpret_cast<uintptr_t>(cin_row) & 15u) == 0)) {
-            __align__(16) OutT r[32];
-            if (cin_row != nullptr) {
-              __align__(16) InT c[32];
-              const uint4* s4 = reinterpret_cast<const uint4*>(cin_row + col0);
-              uint4* c4 = reinterpret_cast<uint4*>(c);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) c4[j] = s4[j];
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                r[j] = from_float<OutT>(fmaf(p.beta, to_float<InT>(c[j]), p.alpha * __uint_as_float(v[j])));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
-            }
-            const uint4* s4 = reinterpret_cast<const uint4*>(r);
-            uint4* d4 = reinterpret_cast<uint4*>(out_b + size_t(row) * p.ldo + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) d4[j] = s4[j];
-            if (out2_b != nullptr) {
-              uint4* e4 = reinterpret_cast<uint4*>(out2_b + size_t(row) * p.ldo + col0);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) e4[j] = s4[j];
-            }
-            uint16_t* stage = mirror_stage + sub * 32 * kMirrorPitch;
-            const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
-            uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) my_row[j] = words[j];
-            __syncwarp();
-            const int seg = lane & 3;  // which 8 of the 32 source rows this lane gathers
+        if (fast_piece(col0, cls)) {
+          __align__(16) OutT r[32];
+          if (cin != nullptr) {
+            // Cin: piece order -> staging tile -> row order
 #pragma unroll
             for (int it = 0; it < 4; ++it) {
-              const int c = (lane >> 2) + 8 * it;  // source column = destination row
-              __align__(16) uint16_t gathered[8];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) gathered[q] = stage[(seg * 8 + q) * kMirrorPitch + c];
-              const size_t at = size_t(col0 + c) * p.ldo + row0 + seg * 8;
-              *reinterpret_cast<uint4*>(out_b + at) = *reinterpret_cast<const uint4*>(gathered);
-              if (out2_b != nullptr) *reinterpret_cast<uint4*>(out2_b + at) = *reinterpret_cast<const uint4*>(gathered);
+              uint32_t* dst = reinterpret_cast<uint32_t*>(stage + (8 * it + piece_row) * kMirrorPitch + piece_col);
+              dst[0] = now[it].x; dst[1] = now[it].y; dst[2] = now[it].z; dst[3] = now[it].w;
             }
             __syncwarp();
-            continue;
-          }
-        }
-        if (!row_ok) continue;
-        __align__(16) InT c[32];
-        if (cin_row != nullptr) {
-          const InT* src = cin_row + col0;
-          if (full && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0)) {
-            const uint4* s4 = reinterpret_cast<const uint4*>(src);
-            uint4* c4 = reinterpret_cast<uint4*>(c);
+            __align__(16) InT c[32];
+            uint32_t* cw = reinterpret_cast<uint32_t*>(c);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) c4[j] = s4[j];
+            for (int j = 0; j < 16; ++j) cw[j] = my_row[j];
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              r[j] = from_float<OutT>(fmaf(p.beta, to_float<InT>(c[j]), p.alpha * __uint_as_float(v[j])));
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) c[j] = (col0 + j < p.n) ? src[j] : InT(0.0f);
+            for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
           }
+          // result: row order -> staging tile
+          const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) my_row[j] = words[j];
+          __syncwarp();
+          // stored as it is, in piece order
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int lr = 8 * it + piece_row;
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(stage + lr * kMirrorPitch + piece_col);
+            uint4 piece = make_uint4(src[0], src[1], src[2], src[3]);
+            const size_t at = size_t(row0 + lr) * p.ldo + col0 + piece_col;
+            *reinterpret_cast<uint4*>(out_b + at) = piece;
+            if constexpr (kSym) {
+              if (out2_b != nullptr) {
+                const int d = row0 + lr - (col0 + piece_col);  // position of the diagonal inside the 8 elements
+                if (d >= 0 && d < 8) {
+                  OutT* e = reinterpret_cast<OutT*>(&piece);
+                  e[d] = from_float<OutT>(to_float<OutT>(e[d]) + p.diag);
+                }
+                *reinterpret_cast<uint4*>(out2_b + at) = piece;
+              }
+            }
+          }
+          if constexpr (kSym) {
+            if (cls == 1) {
+              // stored transposed: gather columns of the staging tile
+              const int seg = lane & 3;
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                const int cc = (lane >> 2) + 8 * it;  // source column = destination row
+                __align__(16) uint16_t gathered[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) gathered[q] = stage[(seg * 8 + q) * kMirrorPitch + cc];
+                const size_t at = size_t(col0 + cc) * p.ldo + row0 + seg * 8;
+                *reinterpret_cast<uint4*>(out_b + at) = *reinterpret_cast<const uint4*>(gathered);
+                if (out2_b != nullptr)
+                  *reinterpret_cast<uint4*>(out2_b + at) = *reinterpret_cast<const uint4*>(gathered);
+              }
+            }
+          }
+          __syncwarp();
+          continue;
         }
+        // ---- pieces at the matrix edge, unaligned operands, symmetrised diagonal pieces: one row per lane
+        if (!row_ok) continue;
         __align__(16) OutT r[32];
         __align__(16) OutT r2[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           float x = p.alpha * __uint_as_float(v[j]);
-          if (cin_row != nullptr) x = fmaf(p.beta, to_float<InT>(c[j]), x);
+          if (cin_row != nullptr && col0 + j < p.n) x = fmaf(p.beta, to_float<InT>(cin_row[col0 + j]), x);
           r[j] = from_float<OutT>(x);
-          if constexpr (kSym) {
-            r2[j] = (row == col0 + j) ? from_float<OutT>(to_float<OutT>(r[j]) + p.diag) : r[j];
-          }
+          if constexpr (kSym) r2[j] = (row == col0 + j) ? from_float<OutT>(to_float<OutT>(r[j]) + p.diag) : r[j];
         }
         OutT* dst = out_b + size_t(row) * p.ldo + col0;
-        if (kSym && side == 0 && p.mirror_diagonal != 0) {
+        if (cls == 3) {
           // A B^T with B != A is symmetric only up to rounding: keep the lower triangle of
-          // the diagonal sub-block and mirror it, so that the stored matrix is exactly symmetric.
+          // the diagonal piece and mirror it, so that the stored matrix is exactly symmetric.
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
             if (col > row || col >= p.n) continue;
@@ -483,35 +522,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           continue;
         }
-        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
-          uint4* d4 = reinterpret_cast<uint4*>(dst);
-          const uint4* s4 = reinterpret_cast<const uint4*>(r);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) d4[j] = s4[j];
-        } else {
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.n) dst[j] = r[j];
-        }
-        if constexpr (kSym) {
-          if (out2_b != nullptr) {
-            OutT* dst2 = out2_b + size_t(row) * p.ldo + col0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst2) & 15u) == 0)) {
-              uint4* d4 = reinterpret_cast<uint4*>(dst2);
-              const uint4* s4 = reinterpret_cast<const uint4*>(r2);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) d4[j] = s4[j];
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) dst2[j] = r2[j];
-            }
-          }
-          if (side == 1) {
-            // Transposed copy of a strictly-lower sub-block (lanes hold consecutive rows).
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.n) {
-                out_b[size_t(col0 + j) * p.ldo + row] = r[j];
-                if (out2_b != nullptr) out2_b[size_t(col0 + j) * p.ldo + row] = r[j];
-              }
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j >= p.n) break;
+          dst[j] = r[j];
+          if constexpr (kSym) {
+            if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col0 + j] = r2[j];
+            if (cls == 1) {
+              out_b[size_t(col0 + j) * p.ldo + row] = r[j];
+              if (out2_b != nullptr) out2_b[size_t(col0 + j) * p.ldo + row] = r[j];
             }
           }
         }
