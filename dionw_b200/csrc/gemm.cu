@@ -2,7 +2,9 @@
 // product schedules built from them.
 #include <mutex>
 
-#include "gemm_sm100.cuh"
+#include <cstdlib>
+
+#include "gemm2_sm100.cuh"
 
 namespace dionw {
 namespace {
@@ -72,6 +74,63 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Param
   return launch_status("gemm_kernel launch");
 }
 
+// Two-CTA tiles (clusters of two CTAs): on when the environment asks for it.
+bool use_cta_pairs() {
+  static const bool on = [] {
+    const char* v = std::getenv("DIONW_GEMM_CTA_PAIRS");
+    return v != nullptr && v[0] == '1';
+  }();
+  return on;
+}
+
+template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
+int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, cudaStream_t stream) {
+  auto kernel = gemm2::gemm2_kernel<InT, OutT, kBMajorMN, kSym>;
+  static bool configured = false;
+  if (!configured) {
+    DIONW_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm2::kSmemBytes)));
+    configured = true;
+  }
+  // Pair tiles are 256 x 256.
+  p.tiles_m = (p.m + gemm2::kPairM - 1) / gemm2::kPairM;
+  p.tiles_n = (p.n + gemm2::kBN - 1) / gemm2::kBN;
+  p.tiles_per_batch = kSym ? p.tiles_m * (p.tiles_m + 1) / 2 : p.tiles_m * p.tiles_n;
+  const int total = p.tiles_per_batch * p.batches;
+  if (total == 0) return DIONW_OK;
+  const int pairs_max = sm_count() / 2;
+  const int pairs = total < pairs_max ? total : pairs_max;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(2 * pairs));
+  config.blockDim = dim3(gemm2::kThreads);
+  config.dynamicSmemBytes = gemm2::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 2;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  static bool reported = false;
+  if (!reported && std::getenv("DIONW_GEMM_DEBUG") != nullptr) {
+    reported = true;
+    int clusters = -1;
+    cudaError_t err = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+    fprintf(stderr, "[dionw] gemm2: max active clusters of 2 = %d (%s), pairs launched = %d, SMs = %d\n", clusters,
+            cudaGetErrorString(err), pairs, sm_count());
+  }
+  count_launch();
+  return check_cuda(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p), "gemm2_kernel launch");
+}
+
+// The one-CTA kernel, or the two-CTA kernel when it is switched on.  The tensor map of B is
+// built by the caller for the variant in use (their B boxes differ).
+template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
+int launch_any(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Params& p, cudaStream_t stream) {
+  if (use_cta_pairs()) return launch2<InT, OutT, kBMajorMN, kSym>(map_a, map_b, p, stream);
+  return launch<InT, OutT, kBMajorMN, kSym>(map_a, map_b, p, stream);
+}
+
 int host_sym_tiles(int tiles_m) {
   const int q = tiles_m / 2;
   return q * (q + 1) + ((tiles_m & 1) ? q + 1 : 0);
@@ -96,7 +155,8 @@ int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, i
     ldb = lda;
     b_batch = a_batch;
   }
-  st = make_map(&map_b, b, dtype, kdim, m, blocks, ldb, b_batch, gemm::kBK, gemm::kBN);
+  st = make_map(&map_b, b, dtype, kdim, m, blocks, ldb, b_batch, gemm::kBK,
+                use_cta_pairs() ? gemm2::kHalfN : gemm::kBN);
   if (st != DIONW_OK) return st;
   gemm::Params p{};
   p.cin = cin;
@@ -118,8 +178,8 @@ int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, i
   p.tiles_per_batch = host_sym_tiles(p.tiles_m);
   p.mirror_diagonal = same ? 0 : 1;
   p.status = device_status_word();
-  if (dtype == DIONW_F16) return launch<__half, __half, false, true>(map_a, map_b, p, stream);
-  return launch<__nv_bfloat16, __nv_bfloat16, false, true>(map_a, map_b, p, stream);
+  if (dtype == DIONW_F16) return launch_any<__half, __half, false, true>(map_a, map_b, p, stream);
+  return launch_any<__nv_bfloat16, __nv_bfloat16, false, true>(map_a, map_b, p, stream);
 }
 
 // C = A B + beta Cin.
@@ -134,7 +194,8 @@ int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int
   int st = make_map(&map_a, a, in_dtype, kdim, m, blocks, lda, a_batch, gemm::kBK, gemm::kBM);
   if (st != DIONW_OK) return st;
   if (b_is_nk) {
-    st = make_map(&map_b, b, in_dtype, kdim, n, blocks, ldb, b_batch, gemm::kBK, gemm::kBN);
+    st = make_map(&map_b, b, in_dtype, kdim, n, blocks, ldb, b_batch, gemm::kBK,
+                  use_cta_pairs() ? gemm2::kHalfN : gemm::kBN);
   } else {
     st = make_map(&map_b, b, in_dtype, n, kdim, blocks, ldb, b_batch, 64, gemm::kBK);
   }
@@ -161,13 +222,13 @@ int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int
   const bool f16 = in_dtype == DIONW_F16;
   const bool out_same = out_dtype == in_dtype;
   if (b_is_nk) {
-    if (f16 && out_same) return launch<__half, __half, false, false>(map_a, map_b, p, stream);
-    if (f16) return launch<__half, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
-    if (out_same) return launch<__nv_bfloat16, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
+    if (f16 && out_same) return launch_any<__half, __half, false, false>(map_a, map_b, p, stream);
+    if (f16) return launch_any<__half, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
+    if (out_same) return launch_any<__nv_bfloat16, __nv_bfloat16, false, false>(map_a, map_b, p, stream);
   } else {
-    if (f16 && out_same) return launch<__half, __half, true, false>(map_a, map_b, p, stream);
-    if (f16) return launch<__half, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
-    if (out_same) return launch<__nv_bfloat16, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
+    if (f16 && out_same) return launch_any<__half, __half, true, false>(map_a, map_b, p, stream);
+    if (f16) return launch_any<__half, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
+    if (out_same) return launch_any<__nv_bfloat16, __nv_bfloat16, true, false>(map_a, map_b, p, stream);
   }
   set_error("batched_gemm: bf16 inputs with an fp16 output are not supported");
   return DIONW_ERR_UNSUPPORTED;

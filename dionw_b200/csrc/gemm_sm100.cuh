@@ -254,6 +254,185 @@ template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // ----------------------------------------------------------------------------
+// epilogue of one accumulator: 128 rows (m_base ..) x 256 columns (n_base ..) of batch
+// ``batch``, read from TMEM at ``tmem_acc`` by the warp that owns sub-partition ``sub``;
+// this warp handles chunks first_chunk .. first_chunk+3 of the eight 32-column chunks.
+// Returns false when the bounded wait for the accumulator ran out.
+// ----------------------------------------------------------------------------
+template <typename InT, typename OutT, bool kSym>
+__device__ __forceinline__ bool epilogue_tile(const Params& p, int batch, int m_base, int n_base, uint32_t tmem_acc,
+                                              uint64_t* acc_full_bar, uint32_t acc_phase, volatile int* abort_flag,
+                                              uint16_t* stage, int sub, int lane, int first_chunk) {
+  const InT* cin = reinterpret_cast<const InT*>(p.cin);
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+  OutT* out2 = reinterpret_cast<OutT*>(p.out2);
+  const int row_in_tile = sub * 32 + lane;
+  const int row = m_base + row_in_tile;
+  const int row0 = m_base + sub * 32;
+  const bool row_ok = row < p.m;
+  const InT* cin_row = cin ? cin + size_t(batch) * p.cin_batch + size_t(row) * p.ldc : nullptr;
+  OutT* out_b = out + size_t(batch) * p.out_batch;
+  OutT* out2_b = out2 ? out2 + size_t(batch) * p.out_batch : nullptr;
+  // Class of the 32 x 32 piece at (row0, col0) under the symmetric schedule:
+  // 0 stored as it is; 1 strictly below the diagonal: stored and stored transposed;
+  // 2 strictly above: skipped (its mirror image writes it); 3 on the diagonal of a
+  // product with B != A: lower triangle stored and mirrored element by element.
+  auto class_of = [&](int col0) -> int {
+    if constexpr (!kSym) return 0;
+    if (col0 + 32 <= row0) return 1;
+    if (col0 >= row0 + 32) return 2;
+    return p.mirror_diagonal != 0 ? 3 : 0;
+  };
+  // Pieces wholly inside the matrix move between global memory and registers in
+  // "piece order": lane l holds 8 consecutive elements of row 8*it + l/4 at column
+  // 8*(l%4), it = 0..3, so one instruction touches 8 rows x 64 contiguous bytes.  The
+  // accumulator arrives in "row order" (lane = row); a 32 x 34 staging tile in shared
+  // memory converts between the two.
+  const bool aligned = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out_b) & 15u) == 0 &&
+                       (out2_b == nullptr || (reinterpret_cast<uintptr_t>(out2_b) & 15u) == 0) &&
+                       (cin == nullptr || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(cin) & 15u) == 0 &&
+                                           (p.cin_batch & 7) == 0));
+  const bool rows_inside = row0 + 32 <= p.m;
+  const int piece_row = lane >> 2, piece_col = (lane & 3) * 8;
+  auto fast_piece = [&](int col0, int cls) { return aligned && rows_inside && col0 + 32 <= p.n && cls != 3; };
+  // The epilogue is a chain of dependent latencies; the Cin piece of the next chunk is
+  // requested before the current chunk is worked on.  (Requesting all four chunks of a
+  // tile up front was measured slower: 48 more live registers for no shorter chain.)
+  uint4 ahead[4];
+  auto prefetch = [&](int chunk) {
+    const int col0 = n_base + chunk * 32;
+    const int cls = class_of(col0);
+    if (cin == nullptr || cls == 2 || !fast_piece(col0, cls)) return;
+    const InT* base = cin + size_t(batch) * p.cin_batch + size_t(row0 + piece_row) * p.ldc + col0 + piece_col;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) ahead[it] = *reinterpret_cast<const uint4*>(base + size_t(8 * it) * p.ldc);
+  };
+  prefetch(first_chunk);   // does not depend on the accumulator: overlaps the wait below
+  if (!mbar_wait(acc_full_bar, acc_phase, abort_flag, p.status)) return false;
+  tc_fence_after();
+  uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
+#pragma unroll 1
+  for (int chunk = first_chunk; chunk < first_chunk + kBN / 64; ++chunk) {
+    const int col0 = n_base + chunk * 32;
+    const int cls = class_of(col0);
+    uint4 now[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) now[j] = ahead[j];
+    if (chunk + 1 < first_chunk + kBN / 64) prefetch(chunk + 1);
+    if (col0 >= p.n) break;       // uniform over the warp
+    if (cls == 2) continue;       // uniform over the warp
+    uint32_t v[32];
+    const uint32_t taddr = tmem_acc + (uint32_t(sub * 32) << 16) + uint32_t(chunk * 32);
+    tmem_load32(taddr, v);
+    if (fast_piece(col0, cls)) {
+      __align__(16) OutT r[32];
+      if (cin != nullptr) {
+        // Cin: piece order -> staging tile -> row order
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          uint32_t* dst = reinterpret_cast<uint32_t*>(stage + (8 * it + piece_row) * kMirrorPitch + piece_col);
+          dst[0] = now[it].x; dst[1] = now[it].y; dst[2] = now[it].z; dst[3] = now[it].w;
+        }
+        __syncwarp();
+        __align__(16) InT c[32];
+        uint32_t* cw = reinterpret_cast<uint32_t*>(c);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) cw[j] = my_row[j];
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          r[j] = from_float<OutT>(fmaf(p.beta, to_float<InT>(c[j]), p.alpha * __uint_as_float(v[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
+      }
+      // result: row order -> staging tile
+      const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) my_row[j] = words[j];
+      __syncwarp();
+      // stored as it is, in piece order
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int lr = 8 * it + piece_row;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(stage + lr * kMirrorPitch + piece_col);
+        uint4 piece = make_uint4(src[0], src[1], src[2], src[3]);
+        const size_t at = size_t(row0 + lr) * p.ldo + col0 + piece_col;
+        *reinterpret_cast<uint4*>(out_b + at) = piece;
+        if constexpr (kSym) {
+          if (out2_b != nullptr) {
+            const int d = row0 + lr - (col0 + piece_col);  // position of the diagonal inside the 8 elements
+            if (d >= 0 && d < 8) {
+              OutT* e = reinterpret_cast<OutT*>(&piece);
+              e[d] = from_float<OutT>(to_float<OutT>(e[d]) + p.diag);
+            }
+            *reinterpret_cast<uint4*>(out2_b + at) = piece;
+          }
+        }
+      }
+      if constexpr (kSym) {
+        if (cls == 1) {
+          // stored transposed: gather columns of the staging tile
+          const int seg = lane & 3;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int cc = (lane >> 2) + 8 * it;  // source column = destination row
+            __align__(16) uint16_t gathered[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) gathered[q] = stage[(seg * 8 + q) * kMirrorPitch + cc];
+            const size_t at = size_t(col0 + cc) * p.ldo + row0 + seg * 8;
+            *reinterpret_cast<uint4*>(out_b + at) = *reinterpret_cast<const uint4*>(gathered);
+            if (out2_b != nullptr)
+              *reinterpret_cast<uint4*>(out2_b + at) = *reinterpret_cast<const uint4*>(gathered);
+          }
+        }
+      }
+      __syncwarp();
+      continue;
+    }
+    // ---- pieces at the matrix edge, unaligned operands, symmetrised diagonal pieces: one row per lane
+    if (!row_ok) continue;
+    __align__(16) OutT r[32];
+    __align__(16) OutT r2[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = p.alpha * __uint_as_float(v[j]);
+      if (cin_row != nullptr && col0 + j < p.n) x = fmaf(p.beta, to_float<InT>(cin_row[col0 + j]), x);
+      r[j] = from_float<OutT>(x);
+      if constexpr (kSym) r2[j] = (row == col0 + j) ? from_float<OutT>(to_float<OutT>(r[j]) + p.diag) : r[j];
+    }
+    OutT* dst = out_b + size_t(row) * p.ldo + col0;
+    if (cls == 3) {
+      // A B^T with B != A is symmetric only up to rounding: keep the lower triangle of
+      // the diagonal piece and mirror it, so that the stored matrix is exactly symmetric.
+      for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col > row || col >= p.n) continue;
+        dst[j] = r[j];
+        if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col] = r2[j];
+        if (col < row) {
+          out_b[size_t(col) * p.ldo + row] = r[j];
+          if (out2_b != nullptr) out2_b[size_t(col) * p.ldo + row] = r[j];
+        }
+      }
+      continue;
+    }
+    for (int j = 0; j < 32; ++j) {
+      if (col0 + j >= p.n) break;
+      dst[j] = r[j];
+      if constexpr (kSym) {
+        if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col0 + j] = r2[j];
+        if (cls == 1) {
+          out_b[size_t(col0 + j) * p.ldo + row] = r[j];
+          if (out2_b != nullptr) out2_b[size_t(col0 + j) * p.ldo + row] = r[j];
+        }
+      }
+    }
+  }
+  return true;
+}
+
+// ----------------------------------------------------------------------------
 // the kernel
 // ----------------------------------------------------------------------------
 template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
@@ -361,10 +540,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int ew = warp - 2;                  // 0..7
     const int sub = warp & 3;                 // TMEM lanes 32*sub .. 32*sub+31
     const int first_chunk = (ew >> 2) * (kBN / 64);
-    const int row_in_tile = sub * 32 + lane;
-    const InT* cin = reinterpret_cast<const InT*>(p.cin);
-    OutT* out = reinterpret_cast<OutT*>(p.out);
-    OutT* out2 = reinterpret_cast<OutT*>(p.out2);
     uint16_t* stage = mirror_stage + ew * 32 * kMirrorPitch;
     uint32_t local = 0;
     bool ok = true;
@@ -372,167 +547,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const Tile tile = kSym ? sym_tile(t, p) : general_tile(t, p);
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      const int row = tile.tm * kBM + row_in_tile;
-      const int row0 = tile.tm * kBM + sub * 32;
-      const bool row_ok = row < p.m;
-      const InT* cin_row = cin ? cin + size_t(tile.batch) * p.cin_batch + size_t(row) * p.ldc : nullptr;
-      OutT* out_b = out + size_t(tile.batch) * p.out_batch;
-      OutT* out2_b = out2 ? out2 + size_t(tile.batch) * p.out_batch : nullptr;
-      // Class of the 32 x 32 piece at (row0, col0) under the symmetric schedule:
-      // 0 stored as it is; 1 strictly below the diagonal: stored and stored transposed;
-      // 2 strictly above: skipped (its mirror image writes it); 3 on the diagonal of a
-      // product with B != A: lower triangle stored and mirrored element by element.
-      auto class_of = [&](int col0) -> int {
-        if constexpr (!kSym) return 0;
-        if (col0 + 32 <= row0) return 1;
-        if (col0 >= row0 + 32) return 2;
-        return p.mirror_diagonal != 0 ? 3 : 0;
-      };
-      // Pieces wholly inside the matrix move between global memory and registers in
-      // "piece order": lane l holds 8 consecutive elements of row 8*it + l/4 at column
-      // 8*(l%4), it = 0..3, so one instruction touches 8 rows x 64 contiguous bytes.  The
-      // accumulator arrives in "row order" (lane = row); a 32 x 34 staging tile in shared
-      // memory converts between the two.
-      const bool aligned = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out_b) & 15u) == 0 &&
-                           (out2_b == nullptr || (reinterpret_cast<uintptr_t>(out2_b) & 15u) == 0) &&
-                           (cin == nullptr || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(cin) & 15u) == 0 &&
-                                               (p.cin_batch & 7) == 0));
-      const bool rows_inside = row0 + 32 <= p.m;
-      const int piece_row = lane >> 2, piece_col = (lane & 3) * 8;
-      auto fast_piece = [&](int col0, int cls) { return aligned && rows_inside && col0 + 32 <= p.n && cls != 3; };
-      // The epilogue is a chain of dependent latencies; the Cin piece of the next chunk is
-      // requested before the current chunk is worked on.  (Requesting all four chunks of a
-      // tile up front was measured slower: 48 more live registers for no shorter chain.)
-      uint4 ahead[4];
-      auto prefetch = [&](int chunk) {
-        const int col0 = tile.tn * kBN + chunk * 32;
-        const int cls = class_of(col0);
-        if (cin == nullptr || cls == 2 || !fast_piece(col0, cls)) return;
-        const InT* base = cin + size_t(tile.batch) * p.cin_batch + size_t(row0 + piece_row) * p.ldc + col0 + piece_col;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) ahead[it] = *reinterpret_cast<const uint4*>(base + size_t(8 * it) * p.ldc);
-      };
-      prefetch(first_chunk);   // does not depend on the accumulator: overlaps the wait below
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
-#pragma unroll 1
-      for (int chunk = first_chunk; chunk < first_chunk + kBN / 64; ++chunk) {
-        const int col0 = tile.tn * kBN + chunk * 32;
-        const int cls = class_of(col0);
-        uint4 now[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) now[j] = ahead[j];
-        if (chunk + 1 < first_chunk + kBN / 64) prefetch(chunk + 1);
-        if (col0 >= p.n) break;       // uniform over the warp
-        if (cls == 2) continue;       // uniform over the warp
-        uint32_t v[32];
-        const uint32_t taddr = tmem_base + (uint32_t(sub * 32) << 16) + acc * uint32_t(kBN) + uint32_t(chunk * 32);
-        tmem_load32(taddr, v);
-        if (fast_piece(col0, cls)) {
-          __align__(16) OutT r[32];
-          if (cin != nullptr) {
-            // Cin: piece order -> staging tile -> row order
-#pragma unroll
-            for (int it = 0; it < 4; ++it) {
-              uint32_t* dst = reinterpret_cast<uint32_t*>(stage + (8 * it + piece_row) * kMirrorPitch + piece_col);
-              dst[0] = now[it].x; dst[1] = now[it].y; dst[2] = now[it].z; dst[3] = now[it].w;
-            }
-            __syncwarp();
-            __align__(16) InT c[32];
-            uint32_t* cw = reinterpret_cast<uint32_t*>(c);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) cw[j] = my_row[j];
-            __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              r[j] = from_float<OutT>(fmaf(p.beta, to_float<InT>(c[j]), p.alpha * __uint_as_float(v[j])));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
-          }
-          // result: row order -> staging tile
-          const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) my_row[j] = words[j];
-          __syncwarp();
-          // stored as it is, in piece order
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int lr = 8 * it + piece_row;
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(stage + lr * kMirrorPitch + piece_col);
-            uint4 piece = make_uint4(src[0], src[1], src[2], src[3]);
-            const size_t at = size_t(row0 + lr) * p.ldo + col0 + piece_col;
-            *reinterpret_cast<uint4*>(out_b + at) = piece;
-            if constexpr (kSym) {
-              if (out2_b != nullptr) {
-                const int d = row0 + lr - (col0 + piece_col);  // position of the diagonal inside the 8 elements
-                if (d >= 0 && d < 8) {
-                  OutT* e = reinterpret_cast<OutT*>(&piece);
-                  e[d] = from_float<OutT>(to_float<OutT>(e[d]) + p.diag);
-                }
-                *reinterpret_cast<uint4*>(out2_b + at) = piece;
-              }
-            }
-          }
-          if constexpr (kSym) {
-            if (cls == 1) {
-              // stored transposed: gather columns of the staging tile
-              const int seg = lane & 3;
-#pragma unroll
-              for (int it = 0; it < 4; ++it) {
-                const int cc = (lane >> 2) + 8 * it;  // source column = destination row
-                __align__(16) uint16_t gathered[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) gathered[q] = stage[(seg * 8 + q) * kMirrorPitch + cc];
-                const size_t at = size_t(col0 + cc) * p.ldo + row0 + seg * 8;
-                *reinterpret_cast<uint4*>(out_b + at) = *reinterpret_cast<const uint4*>(gathered);
-                if (out2_b != nullptr)
-                  *reinterpret_cast<uint4*>(out2_b + at) = *reinterpret_cast<const uint4*>(gathered);
-              }
-            }
-          }
-          __syncwarp();
-          continue;
-        }
-        // ---- pieces at the matrix edge, unaligned operands, symmetrised diagonal pieces: one row per lane
-        if (!row_ok) continue;
-        __align__(16) OutT r[32];
-        __align__(16) OutT r2[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = p.alpha * __uint_as_float(v[j]);
-          if (cin_row != nullptr && col0 + j < p.n) x = fmaf(p.beta, to_float<InT>(cin_row[col0 + j]), x);
-          r[j] = from_float<OutT>(x);
-          if constexpr (kSym) r2[j] = (row == col0 + j) ? from_float<OutT>(to_float<OutT>(r[j]) + p.diag) : r[j];
-        }
-        OutT* dst = out_b + size_t(row) * p.ldo + col0;
-        if (cls == 3) {
-          // A B^T with B != A is symmetric only up to rounding: keep the lower triangle of
-          // the diagonal piece and mirror it, so that the stored matrix is exactly symmetric.
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            if (col > row || col >= p.n) continue;
-            dst[j] = r[j];
-            if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col] = r2[j];
-            if (col < row) {
-              out_b[size_t(col) * p.ldo + row] = r[j];
-              if (out2_b != nullptr) out2_b[size_t(col) * p.ldo + row] = r[j];
-            }
-          }
-          continue;
-        }
-        for (int j = 0; j < 32; ++j) {
-          if (col0 + j >= p.n) break;
-          dst[j] = r[j];
-          if constexpr (kSym) {
-            if (out2_b != nullptr) out2_b[size_t(row) * p.ldo + col0 + j] = r2[j];
-            if (cls == 1) {
-              out_b[size_t(col0 + j) * p.ldo + row] = r[j];
-              if (out2_b != nullptr) out2_b[size_t(col0 + j) * p.ldo + row] = r[j];
-            }
-          }
-        }
+      if (!epilogue_tile<InT, OutT, kSym>(p, tile.batch, tile.tm * kBM, tile.tn * kBN, tmem_base + acc * uint32_t(kBN),
+                                          &acc_full[acc], acc_phase, abort_flag, stage, sub, lane, first_chunk)) {
+        ok = false;
+        break;
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);

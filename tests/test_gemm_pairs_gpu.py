@@ -1,0 +1,88 @@
+"""The two-CTA (cta_group::2) variant of the tcgen05 GEMM, switched on with
+DIONW_GEMM_CTA_PAIRS=1.  The switch is read once per process, so the check runs in a
+child process and compares the products with fp32 torch matmuls, and the Newton-Schulz
+built on them with the one-CTA kernel of this process.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CHILD = r"""
+import math, sys, torch
+from dionw_b200 import _native as nat
+torch.manual_seed(7)
+dev = "cuda"
+worst = 0.0
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm())
+# general products, both layouts of B, ragged edges
+for blocks, m, n, k, nk in [(3, 300, 520, 200, True), (2, 512, 768, 1024, False), (1, 130, 72, 64, True), (5, 256, 256, 4096, False)]:
+    a = (torch.randn(blocks, m, k, device=dev) / math.sqrt(k)).half()
+    if nk:
+        b = torch.randn(blocks, n, k, device=dev).half()
+        want = a.float() @ b.float().transpose(1, 2)
+    else:
+        b = torch.randn(blocks, k, n, device=dev).half()
+        want = a.float() @ b.float()
+    if k % 8 or n % 8:
+        continue
+    out = torch.empty(blocks, m, n, dtype=torch.float16, device=dev)
+    nat.batched_gemm(a, b, out, b_is_nk=nk)
+    worst = max(worst, rel(out, want))
+# symmetric products: A A^T with epilogue operands, and a commuting pair
+for blocks, m, k in [(2, 768, 1024), (1, 304, 520), (4, 256, 512)]:
+    x = (torch.randn(blocks, m, k, device=dev) / math.sqrt(k)).half()
+    g = torch.empty(blocks, m, m, dtype=torch.float16, device=dev)
+    nat.symmetric_product(x, g)
+    worst = max(worst, rel(g, x.float() @ x.float().transpose(1, 2)))
+    assert torch.equal(g, g.transpose(1, 2)), "mirrored output is not symmetric"
+    z = torch.empty_like(g); q = torch.empty_like(g)
+    nat.symmetric_product(g, z, cin=g, alpha=0.5, beta=0.25, out2=q, diag=1.0)
+    want = 0.5 * (g.float() @ g.float()) + 0.25 * g.float()
+    worst = max(worst, rel(z, want))
+    eye = torch.eye(m, device=dev)
+    worst = max(worst, rel(q, z.float() + eye))
+    r = torch.empty_like(g)
+    nat.symmetric_product(g, r, b=z, cin=g, beta=0.5)
+    worst = max(worst, rel(r, g.float() @ z.float() + 0.5 * g.float()))
+    assert torch.equal(r, r.transpose(1, 2))
+# the Gram Newton-Schulz on the pair kernel; the parent compares it with its own
+x = (torch.randn(6, 256, 1024, device=dev, generator=torch.Generator(dev).manual_seed(3)) / 512).half()
+ws = torch.empty(nat.newton_schulz_workspace_bytes(6, 256, 1024, 0), dtype=torch.uint8, device=dev)
+o = torch.empty(6, 256, 1024, dtype=torch.bfloat16, device=dev)
+nat.newton_schulz(x.clone(), o, 256, 1024, 0, ws)
+torch.cuda.synchronize()
+assert nat.device_status() == 0
+torch.save(o.cpu(), sys.argv[1])
+print("WORST", worst)
+"""
+
+
+def test_two_cta_gemm_in_child_process(tmp_path):
+    from dionw_b200 import _native as nat
+
+    out_file = tmp_path / "ns_pairs.pt"
+    env = dict(os.environ, DIONW_GEMM_CTA_PAIRS="1", PYTHONPATH=ROOT)
+    done = subprocess.run([sys.executable, "-c", CHILD, str(out_file)], env=env, capture_output=True, text=True,
+                          timeout=600, cwd=ROOT)
+    assert done.returncode == 0, done.stdout + done.stderr
+    worst = float(done.stdout.strip().split("WORST")[-1])
+    assert worst < 2e-3, worst   # fp16 outputs of fp32-accumulated products
+
+    dev = "cuda"
+    x = (torch.randn(6, 256, 1024, device=dev, generator=torch.Generator(dev).manual_seed(3)) / 512).half()
+    ws = torch.empty(nat.newton_schulz_workspace_bytes(6, 256, 1024, 0), dtype=torch.uint8, device=dev)
+    o = torch.empty(6, 256, 1024, dtype=torch.bfloat16, device=dev)
+    nat.newton_schulz(x.clone(), o, 256, 1024, 0, ws)
+    torch.cuda.synchronize()
+    theirs = torch.load(out_file).to(dev)
+    err = float((o.float() - theirs.float()).norm() / o.float().norm())
+    # same arithmetic per product; only the order of fp32 accumulation inside a tile may differ
+    assert err < 2e-3, err
