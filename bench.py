@@ -242,6 +242,97 @@ def run_reference_arm(args) -> None:
 
 
 # ---------------------------------------------------------------------------
+# the Gram Newton-Schulz microbenchmark (``--config gram-ns``)
+# ---------------------------------------------------------------------------
+NS_SHAPES = ((1024, 1024), (1024, 4096), (4096, 14336), (8192, 28672))
+NS_BATCH = 16
+
+
+def run_ns_microbench(args) -> None:
+    """Batches of 16 bf16 matrices ~N(0,1) scaled to unit Frobenius norm, orthogonalized by the
+    public entry ``gram_polar_express(x, 1e-8)``.  Per shape: device time of the whole call and
+    of the iteration alone (operands already packed), algorithmic TFLOP/s of the iteration and
+    the orthogonality error ``||Y Y^T - I||_F`` of the first matrix."""
+    from dionw_b200 import _native
+    from dionw_b200.newton_schulz import NewtonSchulz, gram_polar_express, newton_schulz_fn, padded, run_iteration
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    _native.library()
+    peaks, peaks_kind = measured_peaks()
+    fn = newton_schulz_fn(NewtonSchulz.GRAM)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches_before = _native.launch_count()
+    rows_out = []
+    for m, n in NS_SHAPES:
+        gen = torch.Generator(device=device).manual_seed(m * 31 + n)
+        x = torch.randn(NS_BATCH, m, n, device=device, generator=gen)
+        x = (x / torch.linalg.matrix_norm(x, keepdim=True)).bfloat16()
+
+        def whole():
+            return gram_polar_express(x, 1e-8)
+
+        packed = torch.empty(NS_BATCH, m, padded(n), dtype=torch.float16, device=device)
+        packed[..., :n] = x
+        scratch = torch.empty(fn.workspace_bytes(NS_BATCH, m, n), dtype=torch.uint8, device=device)
+        work = packed.clone()
+
+        def iteration():
+            work.copy_(packed)
+            return run_iteration(fn, work, m, n, scratch, None)
+
+        def clock(call) -> float:
+            for _ in range(args.warmup):
+                call()
+            times = []
+            for _ in range(args.steps):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                call()
+                end.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(end))
+            return statistics.median(times)
+
+        # the refill of the operand is a 2-byte copy, timed alone and taken off the iteration's time
+        refill = clock(lambda: work.copy_(packed))
+        iter_ms = clock(iteration) - refill
+        whole_ms = clock(whole)
+        y = whole()[0].float()
+        err = float(torch.linalg.matrix_norm(y @ y.T - torch.eye(m, device=device)))
+        flops = NS_BATCH * flops_newton_schulz(m, n)
+        rows_out.append({"shape": [m, n], "batch": NS_BATCH, "call_ms": whole_ms, "iteration_ms": iter_ms,
+                         "TFLOP/s": flops / iter_ms / 1e9, "frac_of_burst_peak": flops / iter_ms / 1e9 / peaks["bf16_tflops"],
+                         "orthogonality_error": err, "error_per_sqrt_m": err / m**0.5})
+        del x, packed, scratch, work, y
+        torch.cuda.empty_cache()
+    launches = _native.launch_count() - launches_before
+    clocks = sampler.stop()
+    big = rows_out[-1]
+    total_flops = sum(NS_BATCH * flops_newton_schulz(m, n) for m, n in NS_SHAPES)
+    total_ms = sum(r["iteration_ms"] for r in rows_out)
+    line = {
+        "metric": "gram_newton_schulz_tflops", "value": total_flops / total_ms / 1e9, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp16 iteration, fp32 accumulate, bf16 result", "data": "synthetic",
+        "config": {"workload": "Gram Newton-Schulz, batches of 16 at 1024x1024, 1024x4096, 4096x14336, 8192x28672",
+                   "l2": "operands of the two large shapes exceed L2; medians of per-call CUDA-event times"},
+        "roofline": {"kernel": f"gemm_kernel (products of the {big['shape'][0]}x{big['shape'][1]} batch)",
+                     "bound": "tensor", "achieved": big["TFLOP/s"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": big["TFLOP/s"] / peaks["bf16_tflops"], "traffic": None,
+                     "peak_kind": f"{peaks_kind} bf16 cuBLAS, burst (each batch is timed alone)"},
+        "shapes": rows_out, "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
 # the GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu_arm(args) -> None:
@@ -417,12 +508,17 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
-    parser.add_argument("--config", choices=sorted(CONFIGS), default="llama3-8b")
+    parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.config == "gram-ns":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the gram-ns microbenchmark has no CPU arm"}))
+        else:
+            run_ns_microbench(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

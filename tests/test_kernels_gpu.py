@@ -292,6 +292,56 @@ def test_mirrored_gram_products_stay_within_the_rounding_of_the_full_ones(native
     assert err_m < 1.2 * err_f + 0.05
 
 
+def _unit_bf16_batch(batch: int, m: int, n: int, seed: int) -> torch.Tensor:
+    """The microbenchmark's input: N(0,1) entries, each matrix scaled to unit Frobenius norm, bf16."""
+    x = torch.randn(batch, m, n, generator=_gen(seed))
+    return (x / torch.linalg.matrix_norm(x, keepdim=True)).bfloat16()
+
+
+@pytest.mark.parametrize("m,n", [(1024, 1024), (1024, 4096)])
+def test_microbenchmark_batches_match_oracle_through_the_public_entry(native, m, n) -> None:
+    """Batches of 16 bf16 matrices of unit Frobenius norm through ``gram_polar_express(x, 1e-8)``:
+    the polar factors and the orthogonality error ``||Y Y^T - I||_F`` of two of the sixteen are
+    compared with the CPU oracle, and every matrix of the batch must reach the same error level."""
+    from dionw_b200.newton_schulz import gram_polar_express
+
+    x = _unit_bf16_batch(16, m, n, seed=m + n)
+    ours = gram_polar_express(x.to(DEV), 1e-8)
+    assert native.device_status() == 0
+    assert ours.dtype == torch.bfloat16 and ours.shape == x.shape
+    ours = ours.float().cpu()
+    torch.set_num_threads(8)
+    expect = oracle.gram_newton_schulz(x[:2].float()).float()
+    assert rel_l2(ours[:2], expect) < 5e-3
+    eye = torch.eye(m, dtype=torch.float64)
+    ref_err = [float((expect[i].double() @ expect[i].double().T - eye).norm()) for i in range(2)]
+    our_err = [float((ours[i].double() @ ours[i].double().T - eye).norm()) for i in range(16)]
+    for i in range(2):
+        assert abs(our_err[i] - ref_err[i]) < 0.05 * ref_err[i] + 0.05
+    assert max(our_err) < 1.2 * max(ref_err) + 0.05
+
+
+def test_microbenchmark_large_shape_reaches_the_small_shapes_orthogonality(native) -> None:
+    """4096 x 14336 (the oracle would take minutes): the error per sqrt(rows) is a property of
+    the five fixed polynomial steps and the aspect ratio, not of the size, so it must stay at
+    the level the 1024 x 3584 case (same aspect ratio) reaches on the oracle."""
+    from dionw_b200.newton_schulz import gram_polar_express
+
+    small = _unit_bf16_batch(1, 1024, 3584, seed=5)
+    torch.set_num_threads(8)
+    expect = oracle.gram_newton_schulz(small.float()).double()[0]
+    level = float((expect @ expect.T - torch.eye(1024, dtype=torch.float64)).norm()) / 1024**0.5
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    big = torch.randn(2, 4096, 14336, device=DEV, generator=gen)
+    big = (big / torch.linalg.matrix_norm(big, keepdim=True)).bfloat16()
+    y = gram_polar_express(big, 1e-8).float()
+    assert native.device_status() == 0
+    eye = torch.eye(4096, device=DEV)
+    for i in range(2):
+        err = float(torch.linalg.matrix_norm(y[i] @ y[i].T - eye)) / 4096**0.5
+        assert err < 1.25 * level + 0.01, (err, level)
+
+
 @pytest.mark.parametrize("kind,name", [(1, "polar_express_triton"), (2, "keller_triton")])
 @pytest.mark.parametrize("tag", ["wide", "tall", "square"])
 def test_bf16_iterations_match_reference_fixture(native, kind, name, tag) -> None:
