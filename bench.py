@@ -40,7 +40,14 @@ CONFIGS = {
     "llama3-8b": (32, 4096, 1024, 14336, 128256),
     "llama3-8b-2layers": (2, 4096, 1024, 14336, 16032),
     "tiny": (2, 1024, 256, 3584, 4096),
+    # 20-layer slice of the Llama-3-70B shapes, embedding only, GPU EMA (decay 0.9999): 8 GPUs
+    "llama3-70b-20layers": (20, 8192, 1024, 28672, 128256),
+    "llama3-70b-1layer": (1, 8192, 1024, 28672, 16032),
 }
+EMBED_ONLY_WITH_EMA = {"llama3-70b-20layers", "llama3-70b-1layer"}
+# Above this many bytes of fp32 weights + gradients per GPU the gradients are one tensor per
+# shape, shared by all layers (the step reads them, never writes them).
+SHARED_GRADS_ABOVE = 120e9
 
 
 # ---------------------------------------------------------------------------
@@ -65,7 +72,7 @@ class LlamaShaped(nn.Module):
         self.embed = nn.Embedding(vocab, d, device=device)
         self.layers = nn.ModuleList(Layer(d, dkv, dff, device) for _ in range(layers))
         self.norm = nn.Parameter(torch.empty(d, device=device))
-        self.lm_head = nn.Linear(d, vocab, bias=False, device=device)
+        self.lm_head = None if name in EMBED_ONLY_WITH_EMA else nn.Linear(d, vocab, bias=False, device=device)
 
     @torch.no_grad()
     def init_(self, seed: int) -> None:
@@ -99,7 +106,7 @@ def census(model: LlamaShaped, fraction: float = 0.25, min_dim: int = 1024) -> d
     return {
         "matrix_elements": e, "selected_elements": es, "adamw_elements": adam, "ns_flops": ns,
         "bytes_accumulate": 12 * e, "bytes_pack": 10 * es, "bytes_finish": 2 * es,
-        "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam,
+        "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam, "bytes_ema": 12 * (e + adam),
     }
 
 
@@ -353,23 +360,32 @@ def run_gpu_arm(args) -> None:
 
     model = LlamaShaped(args.config, device)
     model.init_(seed=0)
-    routes = {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
+    routes = {} if model.lm_head is None else {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
     groups, _ = dionw.param_groups(model, routes=routes)
+    ema = dionw.EMAConfig(decay=0.9999, device=dionw.EMADevice.GPU) if args.config in EMBED_ONLY_WITH_EMA else None
     if distributed:
         from dionw_b200.distributed import ShardedDion
 
-        optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+        optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
         if args.no_overlap:
             optimizer.overlap_apply = False
         if args.round_elements:
             optimizer.round_elements = args.round_elements
     else:
-        optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+        optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
     if args.no_overlap:
         optimizer.overlap_streams = False
     gen = torch.Generator(device=device).manual_seed(1)
+    param_bytes = sum(p.numel() * 4 for p in model.parameters())
+    shared_grads = 2 * param_bytes > SHARED_GRADS_ABOVE
+    by_shape: dict[tuple, torch.Tensor] = {}
     for p in model.parameters():
-        p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
+        if shared_grads:
+            if tuple(p.shape) not in by_shape:
+                by_shape[tuple(p.shape)] = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
+            p.grad = by_shape[tuple(p.shape)]
+        else:
+            p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
     work = census(model)
 
     def barrier() -> None:
@@ -387,6 +403,14 @@ def run_gpu_arm(args) -> None:
 
     import dionw_b200.optimizer as optimizer_module
     optimizer_module.adamw_step = timed_adamw
+    if optimizer.ema is not None:
+        real_flush = optimizer.ema._flush_gpu
+
+        def timed_flush():
+            with timer("ema"):
+                real_flush()
+
+        optimizer.ema._flush_gpu = timed_flush
 
     for _ in range(args.warmup):
         optimizer.step()
@@ -475,6 +499,8 @@ def run_gpu_arm(args) -> None:
         "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
         "hbm_peak_GB/s": peaks["hbm_gbs"],
     }
+    if "ema" in stages:
+        stage_report["ema"] = {"ms": stages["ema"], "GB/s": gbs("bytes_ema", "ema", share)}
     cpu = cpu_sample_step(args.config, 5, 1) if world == 1 and not args.no_cpu_baseline else None
     line = {
         "metric": "optimizer_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
@@ -482,7 +508,10 @@ def run_gpu_arm(args) -> None:
         "vs_baseline": None, "dtype": "fp32 state, fp16 Newton-Schulz (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
                    "lr": LR, "weight_decay": WEIGHT_DECAY, "l2": "working set >> L2 (126 MB), no flush needed",
-                   "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)"},
+                   "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)",
+                   "ema": "GPU shadows, decay 0.9999, every step" if ema is not None else None,
+                   "gradients": ("one tensor per shape shared by all layers (weights + gradients would not fit "
+                                 "beside the state)" if shared_grads else "one tensor per parameter")},
         "roofline": {
             "kernel": "gemm_kernel (all Newton-Schulz products of a step)",
             "bound": "tensor", "achieved": ns_tflops, "peak": peak_tf, "unit": "TFLOP/s",

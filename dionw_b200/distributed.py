@@ -16,7 +16,11 @@ sharded is the optimizer's work and state:
   the same kernel and the same inputs, so replicas stay bit-identical;
 * large AdamW tensors are cut into ``world`` equal element ranges: each rank
   updates its range (moments exist only for it) and an in-place all-gather
-  rebuilds the parameter; small ones are updated on every rank.
+  rebuilds the parameter; small ones are updated on every rank;
+* the EMA (``ema=EMAConfig(...)``) keeps, of every large parameter, the shadow of
+  this rank's element range only: replicas are identical after the step, so each
+  rank averages its range with no communication, on the GPU or through the
+  pinned-host worker; small parameters keep whole shadows on every rank.
 
 The all-gather of round t is in flight while round t+1 computes (two scratch
 arenas alternate).  Received data is in local memory before any kernel reads it;
@@ -37,9 +41,10 @@ from dionw_b200 import _matrix_step, _native, _workspace
 from dionw_b200._adamw import init_adamw_state
 from dionw_b200._buckets import Bucket, block_shape, build_buckets
 from dionw_b200._keys import (
-    ADAMW_STEP_STATE, EXP_AVG_SQ_STATE, EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_STATE, NUM_HEADS_KEY, ROUTE_KEY,
-    VARIANCE_STATE,
+    ADAMW_STEP_STATE, EMA_SHADOW, EXP_AVG_SQ_STATE, EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_STATE, NUM_HEADS_KEY,
+    ROUTE_KEY, VARIANCE_STATE,
 )
+from dionw_b200.ema import EMAConfig, IntegratedEMAOptimizer, ProfileRegion, no_profile
 from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate
 from dionw_b200.optimizer import _DionCore
 from dionw_b200.routing import RouteKind
@@ -130,15 +135,8 @@ class _Round:
     group: dict[str, Any]
 
 
-class ShardedDion(_DionCore):
-    """``Dion`` with work and state sharded over the ranks of ``process_group``.
-
-    Same arguments as ``Dion`` (no EMA here).  Every rank must hold identical
-    parameters and, at each step, identical gradients; after the step the
-    parameters are again identical on every rank, and equal bit for bit to what
-    a single-GPU ``Dion`` computes.  ``state_dict()`` returns the single-GPU
-    layout on every rank (it gathers); ``load_state_dict()`` takes that layout.
-    """
+class _ShardedCore(_DionCore):
+    """The sharded step and its checkpoint layout, without the EMA."""
 
     def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
                  muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.0,
@@ -209,10 +207,11 @@ class ShardedDion(_DionCore):
             shared[(bucket.group_index, bucket.rows, bucket.cols, bucket.params[0].device)].local = bucket
         mine = {id(p) for ps in owned.values() for p in ps}
         for sb in shared.values():
-            for param in sb.params:  # a loaded checkpoint leaves full state everywhere: keep the owner's only
-                if id(param) not in mine and param in self.state:
-                    self.state[param].pop(MOMENTUM_STATE, None)
-                    self.state[param].pop(VARIANCE_STATE, None)
+            for param in sb.params:
+                entry = self.state[param]   # every rank keeps an entry: the EMA hangs its shadow there
+                if id(param) not in mine:   # a loaded checkpoint leaves full state everywhere: keep the owner's only
+                    entry.pop(MOMENTUM_STATE, None)
+                    entry.pop(VARIANCE_STATE, None)
         self._shared = list(shared.values())
         self._buckets = [sb.local for sb in self._shared if sb.local is not None]
         return self._shared
@@ -394,10 +393,32 @@ class ShardedDion(_DionCore):
                         whole = torch.empty_like(param)
                         dist.all_gather_into_tensor(whole.view(-1), self.state[param][key], group=self._pg)
                         entry[key] = whole
+                shard = self.state.get(param, {}).get(EMA_SHADOW)
+                if shard is not None and self._ema_is_cut(param):
+                    entry[EMA_SHADOW] = self._gather_shadow(param, shard)
                 if entry:
                     packed["state"][index] = entry
                 index += 1
         return packed
+
+    # ---- EMA shards ------------------------------------------------------------
+    def _ema_is_cut(self, param: Tensor) -> bool:
+        """Whether the EMA keeps only this rank's element range of ``param``'s shadow."""
+        n = param.numel()   # ranges of a multiple of four floats keep every range 16-byte aligned
+        return (self._world > 1 and n >= ADAMW_SHARD_MIN_ELEMENTS and n % (4 * self._world) == 0
+                and param.is_contiguous())
+
+    def _ema_view(self, param: Tensor) -> Tensor:
+        if not self._ema_is_cut(param):
+            return param
+        start, stop = shard_range(param.numel(), self._rank, self._world)
+        return param.detach().view(-1)[start:stop]
+
+    def _gather_shadow(self, param: Tensor, shard: Tensor) -> Tensor:
+        """The whole shadow, in the parameter's shape, on the shard's device (a collective call)."""
+        whole = torch.empty(param.shape, dtype=shard.dtype, device=param.device)
+        self._dist.all_gather_into_tensor(whole.view(-1), shard.to(param.device).contiguous(), group=self._pg)
+        return whole if shard.device == param.device else whole.to(shard.device)
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         """Takes the single-GPU layout; each rank keeps its own share of it."""
@@ -414,3 +435,47 @@ class ShardedDion(_DionCore):
                 for key in (EXP_AVG_STATE, EXP_AVG_SQ_STATE):
                     if entry[key].numel() == param.numel():
                         entry[key] = entry[key].reshape(-1)[start:stop].clone()
+
+
+class ShardedDion(IntegratedEMAOptimizer, _ShardedCore):
+    """``Dion`` with work and state sharded over the ranks of ``process_group``.
+
+    Same arguments as ``Dion``.  Every rank must hold identical parameters and, at
+    each step, identical gradients; after the step the parameters are again
+    identical on every rank, and equal bit for bit to what a single-GPU ``Dion``
+    computes.  ``state_dict()`` returns the single-GPU layout on every rank (it
+    gathers; a collective call); ``load_state_dict()`` takes that layout and keeps
+    this rank's share.  ``swap_ema_weights`` / ``restore_non_ema_weights`` are
+    collective calls too: shadow ranges are all-gathered straight into the parameters.
+    """
+
+    def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
+                 muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.0,
+                 eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE, process_group: Any = None,
+                 ema: EMAConfig | None = None, profile_region: ProfileRegion = no_profile) -> None:
+        super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
+                         weight_decay=weight_decay, eps=eps, matrix_update=matrix_update,
+                         process_group=process_group)
+        self._init_integrated_ema(ema, profile_region)
+        if self._ema_helper is not None:
+            self._ema_helper.source_view = self._ema_view
+
+    def _loaded_shadow_share(self, param: Tensor, shadow: Tensor) -> Tensor:
+        if not self._ema_is_cut(param) or shadow.numel() != param.numel():
+            return shadow
+        start, stop = shard_range(param.numel(), self._rank, self._world)
+        return shadow.reshape(-1)[start:stop]
+
+    def _swap_in(self, param: Tensor, shadow: Tensor) -> Tensor:
+        if not self._ema_is_cut(param):
+            return super()._swap_in(param, shadow)
+        kept = self._ema_view(param).clone()
+        self._dist.all_gather_into_tensor(param.data.view(-1), shadow.to(device=param.device, dtype=param.dtype),
+                                          group=self._pg)
+        return kept
+
+    def _swap_out(self, param: Tensor, kept: Tensor) -> None:
+        if not self._ema_is_cut(param):
+            super()._swap_out(param, kept)
+            return
+        self._dist.all_gather_into_tensor(param.data.view(-1), kept, group=self._pg)

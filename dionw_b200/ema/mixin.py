@@ -142,12 +142,17 @@ class IntegratedEMAOptimizer(Optimizer):
                 if not isinstance(shadow, Tensor):
                     raise TypeError(f"{name} EMA shadow must be a tensor")
                 entry = self.state[param]
+                shadow = self._loaded_shadow_share(param, shadow)
                 entry[EMA_SHADOW] = torch.empty_like(
                     shadow, device=param.device if on_gpu else torch.device("cpu"), dtype=FP32,
                     pin_memory=pin).copy_(shadow)
                 entry[EMA_INITIALIZED] = source[EMA_INITIALIZED]
                 entry[EMA_PENDING] = False
         helper.step_count = count
+
+    def _loaded_shadow_share(self, param: Tensor, shadow: Tensor) -> Tensor:
+        """The part of a checkpoint's shadow this optimizer keeps (all of it, unless sharded)."""
+        return shadow
 
     # ---- evaluation with EMA weights ----------------------------------------
     @torch.no_grad()
@@ -200,9 +205,17 @@ class IntegratedEMAOptimizer(Optimizer):
                 f"{context} EMA swap found {len(pairs)} initialized shadows for {len(params)} parameters. "
                 "Refusing to mix live and EMA weights.")
         for param, shadow in pairs:
-            self._stored_params[id(param)] = param.data.clone()
-            param.data.copy_(shadow.to(device=param.device, dtype=param.dtype))
+            self._stored_params[id(param)] = self._swap_in(param, shadow)
         return True
+
+    def _swap_in(self, param: Tensor, shadow: Tensor) -> Tensor:
+        """Write ``shadow`` into ``param``; returns what ``_swap_out`` needs to undo it."""
+        kept = param.data.clone()
+        param.data.copy_(shadow.to(device=param.device, dtype=param.dtype))
+        return kept
+
+    def _swap_out(self, param: Tensor, kept: Tensor) -> None:
+        param.data.copy_(kept)
 
     @torch.no_grad()
     def restore_non_ema_weights(self) -> bool:
@@ -212,6 +225,6 @@ class IntegratedEMAOptimizer(Optimizer):
         for param in self._iter_trainable_params():
             kept = self._stored_params.get(id(param))
             if kept is not None:
-                param.data.copy_(kept)
+                self._swap_out(param, kept)
         self._stored_params.clear()
         return True

@@ -11,6 +11,7 @@ on the device (a stream dependency), not on the host.
 from __future__ import annotations
 
 import os
+from collections.abc import Callable
 from typing import TYPE_CHECKING, Any
 
 import torch
@@ -54,6 +55,9 @@ class OptimizerIntegratedEMA:
         self._snapshot_event: torch.cuda.Event | None = None
         self._copy_streams: dict[torch.device, torch.cuda.Stream] = {}
         self._threads = max(1, min(16, (os.cpu_count() or 2) // 2))
+        # What of a parameter this tracker follows: the whole tensor, unless the owning
+        # optimizer keeps only a slice of each shadow (an optimizer sharded over ranks).
+        self.source_view: Callable[[Tensor], Tensor] = lambda param: param
 
     # ---- schedule ---------------------------------------------------------
     @property
@@ -106,17 +110,18 @@ class OptimizerIntegratedEMA:
             state = self.optimizer.state[param]
             if EMA_SHADOW not in state:
                 self._new_shadow(param, state)
+            source = self.source_view(param)
             if self._on_gpu:
                 if self._reseed or not state[EMA_INITIALIZED]:
-                    self._copy_queue.append((state[EMA_SHADOW], param))
+                    self._copy_queue.append((state[EMA_SHADOW], source))
                     state[EMA_INITIALIZED] = True
                 else:
-                    self._lerp_queue.append((state[EMA_SHADOW], param))
+                    self._lerp_queue.append((state[EMA_SHADOW], source))
                 state[EMA_PENDING] = False
             else:
                 if self._reseed:
                     state[EMA_INITIALIZED] = False
-                self._staged.append((param, state))
+                self._staged.append((source, state))
                 state[EMA_PENDING] = True
 
     def _new_shadow(self, param: Tensor, state: dict[str, Any]) -> None:
@@ -124,7 +129,8 @@ class OptimizerIntegratedEMA:
             raise ValueError("EMA configured for the GPU but a parameter is on the CPU")
         pin = self.config.pin_memory and not self._on_gpu
         state[EMA_SHADOW] = torch.zeros_like(
-            param, dtype=FP32, device=param.device if self._on_gpu else torch.device("cpu"), pin_memory=pin)
+            self.source_view(param), dtype=FP32, device=param.device if self._on_gpu else torch.device("cpu"),
+            pin_memory=pin)
         state[EMA_INITIALIZED] = False
 
     # ---- applying ---------------------------------------------------------

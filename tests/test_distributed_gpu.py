@@ -89,15 +89,106 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_sharded_step_equals_single_gpu_step() -> None:
+def _ema_worker(rank: int, world: int, port: int, failures, ema_device: str) -> None:
+    import torch.distributed as dist
+
+    import dionw_b200 as dionw
+    from dionw_b200.distributed import ShardedDion
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        config = dionw.EMAConfig(decay=0.9, device=dionw.EMADevice(ema_device), update_every_n_steps=1)
+
+        def build(cls):
+            net = _model(device)
+            net.wide = nn.Parameter(torch.randn(1024, 1024, generator=torch.Generator().manual_seed(5)).to(device) * 0.02)
+            groups, _ = dionw.param_groups(net, fraction=0.25, selection_min_dim=128)
+            return net, cls(groups, lr=3e-4, weight_decay=0.05, ema=config)
+
+        single_net, single = build(dionw.Dion)
+        sharded_net, sharded = build(ShardedDion)
+        for step in range(3):
+            _grads(single_net, step)
+            _grads(sharded_net, step)
+            single.step()
+            sharded.step()
+        # large parameters keep this rank's range of the shadow only, small ones the whole
+        for name in ("wide", "big.weight"):
+            p = dict(sharded_net.named_parameters())[name]
+            shadow = sharded.state[p]["ema_shadow"]
+            assert shadow.numel() == p.numel() // world, name
+            assert shadow.is_cuda == (ema_device == "gpu")
+        assert sharded.state[sharded_net.norm]["ema_shadow"].shape == sharded_net.norm.shape
+        # the gathered checkpoint equals the single-GPU one, shadows included
+        want, got = single.state_dict(), sharded.state_dict()
+        assert want["_ema_step_count"] == got["_ema_step_count"] == 3
+        assert set(want["state"]) == set(got["state"])
+        for index, entry in want["state"].items():
+            assert set(entry) == set(got["state"][index]), index
+            for key, value in entry.items():
+                mine = got["state"][index][key]
+                if isinstance(value, torch.Tensor):
+                    assert value.device == mine.device and value.shape == mine.shape, (index, key)
+                    assert torch.equal(value, mine), (index, key)
+                else:
+                    assert value == mine, (index, key)
+        # evaluation weights: swap (a collective), compare, restore
+        live = [p.detach().clone() for p in sharded_net.parameters()]
+        assert single.swap_ema_weights() and sharded.swap_ema_weights()
+        for a, b in zip(single_net.parameters(), sharded_net.parameters()):
+            assert torch.equal(a, b), "swapped weights differ"
+        assert sharded.ema_weights_swapped
+        single.restore_non_ema_weights()
+        sharded.restore_non_ema_weights()
+        for a, b in zip(live, sharded_net.parameters()):
+            assert torch.equal(a, b), "restored weights differ"
+        # resume from the gathered checkpoint and continue identically
+        resumed_net, resumed = build(ShardedDion)
+        resumed_net.load_state_dict(sharded_net.state_dict())
+        resumed.load_state_dict({**got, "state": {i: {k: (v.clone() if isinstance(v, torch.Tensor) else v)
+                                                      for k, v in e.items()} for i, e in got["state"].items()}})
+        wide = resumed.state[resumed_net.wide]["ema_shadow"]
+        assert wide.numel() == 1024 * 1024 // world and wide.is_cuda == (ema_device == "gpu")
+        for net, opt in ((single_net, single), (resumed_net, resumed)):
+            _grads(net, 3)
+            opt.step()
+        want, got = single.state_dict(), resumed.state_dict()
+        for index, entry in want["state"].items():
+            for key, value in entry.items():
+                if isinstance(value, torch.Tensor):
+                    assert torch.equal(value, got["state"][index][key]), ("resumed", index, key)
+        torch.cuda.synchronize()
+    except Exception as exc:  # reported to the parent
+        import traceback
+        failures.put(f"rank {rank}: {exc!r}\n{traceback.format_exc()}")
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_two_ranks(target, *extra) -> None:
     ctx = mp.get_context("spawn")
     failures = ctx.Queue()
     port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, failures)) for r in range(2)]
+    procs = [ctx.Process(target=target, args=(r, 2, port, failures, *extra)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(300)
     assert failures.empty(), failures.get()
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_step_equals_single_gpu_step() -> None:
+    _run_two_ranks(_worker)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("ema_device", ["gpu", "cpu"])
+def test_sharded_ema_equals_single_gpu_ema(ema_device) -> None:
+    """Each rank averages its element range of the large parameters; gathered, the shadows,
+    the swapped-in evaluation weights and a resumed run equal the single-GPU optimizer's."""
+    _run_two_ranks(_ema_worker, ema_device)
