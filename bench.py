@@ -89,9 +89,20 @@ def flops_newton_schulz(m: int, n: int) -> float:
     return 2.0 * (3.0 * m * m * n + 11.5 * m**3)
 
 
+# DRAM bytes the products of one Gram Newton-Schulz move for an m x n operand: the operand census
+# 2 B x (6 m n + 40 m^2) (every product reads its operands and writes its result once) times 1.03,
+# the ratio an ncu capture of the 18 products of four 3584 x 4096 blocks measured against it
+# (1.240 GB per block; dram__bytes_read.sum + dram__bytes_write.sum).
+NS_TRAFFIC_CALIBRATION = 1.03
+
+
+def traffic_newton_schulz(m: int, n: int) -> float:
+    return NS_TRAFFIC_CALIBRATION * 2.0 * (6.0 * m * n + 40.0 * m * m)
+
+
 def census(model: LlamaShaped, fraction: float = 0.25, min_dim: int = 1024) -> dict[str, float]:
     """Algorithmic work of one step: elements, bytes per pass, Newton-Schulz FLOPs."""
-    e = es = ns = adam = 0.0
+    e = es = ns = adam = ns_traffic = 0.0
     for layer in model.layers:
         for w in (layer.q, layer.k, layer.v, layer.o, layer.gate, layer.up, layer.down):
             rows, cols = w.shape
@@ -100,11 +111,13 @@ def census(model: LlamaShaped, fraction: float = 0.25, min_dim: int = 1024) -> d
             e += rows * cols
             es += k * cols
             ns += flops_newton_schulz(min(k, cols), max(k, cols))
+            ns_traffic += traffic_newton_schulz(min(k, cols), max(k, cols))
     for p in model.parameters():
         adam += p.numel()
     adam -= e
     return {
         "matrix_elements": e, "selected_elements": es, "adamw_elements": adam, "ns_flops": ns,
+        "ns_traffic": ns_traffic,
         "bytes_accumulate": 12 * e, "bytes_pack": 10 * es, "bytes_finish": 2 * es,
         "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam, "bytes_ema": 12 * (e + adam),
     }
@@ -444,6 +457,17 @@ def run_gpu_arm(args) -> None:
     stages = {k: v / stage_steps for k, v in timer.collect().items()}
     timer.enabled = False
 
+    # ---- host dispatch: wall time for step() to return with the GPU idle at the start and
+    # no synchronize inside (one step's launches fit the driver's launch queue)
+    host_times = []
+    for _ in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        optimizer.step()
+        host_times.append((time.perf_counter() - t0) * 1e3)
+    barrier()
+    host_ms = statistics.median(host_times)
+
     # ---- end to end: gradients come from pinned host memory, one scalar goes back
     pool: dict[tuple, torch.Tensor] = {}
     for p in model.parameters():
@@ -515,7 +539,10 @@ def run_gpu_arm(args) -> None:
         "roofline": {
             "kernel": "gemm_kernel (all Newton-Schulz products of a step)",
             "bound": "tensor", "achieved": ns_tflops, "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": ns_tflops / peak_tf if ns_tflops else None, "traffic": None,
+            "frac": ns_tflops / peak_tf if ns_tflops else None, "traffic": work["ns_traffic"] * share,
+            "traffic_kind": ("DRAM bytes of all gemm_kernel launches of one step on this rank: the operand census "
+                             "of the products, calibrated x1.03 on an ncu capture of the 18 products of four "
+                             "3584x4096 blocks and scaled by blocks (traffic grows with the blocks processed)"),
             "peak_kind": f"{peaks_kind} bf16 cuBLAS, sustained (the kernel is timed inside the step)",
             "flops_per_step": work["ns_flops"] * share,
         },
@@ -524,6 +551,7 @@ def run_gpu_arm(args) -> None:
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
                 "steps": e2e_steps},
         "gpu_launches": launches,
+        "host_dispatch_ms": host_ms,
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
