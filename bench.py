@@ -382,6 +382,8 @@ def run_gpu_arm(args) -> None:
         optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
         if args.no_overlap:
             optimizer.overlap_apply = False
+        if args.overlap_apply:
+            optimizer.overlap_apply = True
         if args.round_elements:
             optimizer.round_elements = args.round_elements
     else:
@@ -533,6 +535,8 @@ def run_gpu_arm(args) -> None:
         "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
                    "lr": LR, "weight_decay": WEIGHT_DECAY, "l2": "working set >> L2 (126 MB), no flush needed",
                    "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)",
+                   "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
+                                     "round_elements": int(optimizer.round_elements)} if distributed else None),
                    "ema": "GPU shadows, decay 0.9999, every step" if ema is not None else None,
                    "gradients": ("one tensor per shape shared by all layers (weights + gradients would not fit "
                                  "beside the state)" if shared_grads else "one tensor per parameter")},
@@ -569,6 +573,8 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
+    parser.add_argument("--overlap-apply", action="store_true",
+                        help="sharded step: weight update of a round on a side stream beside the next round")
     args = parser.parse_args()
     if args.config == "gram-ns":
         if args.impl == "reference":

@@ -368,34 +368,46 @@ pack_rows_kernel(float* __restrict__ src, const int32_t* __restrict__ index, con
   } else {
     denom = __fadd_rn(frob[b], eps);
   }
-  for (long long e = 4LL * lane; e < cols; e += 128) {
-    float v[4];
-    load4f(m, vec, e, cols, v);
-    uint16_t h[4];
+  // Four 16-byte loads per lane are requested before the first is used: a warp keeps 2 KB of
+  // the row in flight, which is what the stream needs to approach the memory rate.
+  constexpr int kUnroll = 4;
+  for (long long e0 = 4LL * lane; e0 < cols; e0 += 128 * kUnroll) {
+    float v[kUnroll][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (kBf16) {
-        const __nv_bfloat16 r = __float2bfloat16_rn(__fdiv_rn(bf16_round(v[i]), denom));
-        h[i] = *reinterpret_cast<const uint16_t*>(&r);
-      } else {
-        const __half r = __float2half_rn(__fdiv_rn(v[i], denom));
-        h[i] = *reinterpret_cast<const uint16_t*>(&r);
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long e = e0 + 128LL * u;
+      if (e < cols) load4f(m, vec, e, cols, v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long e = e0 + 128LL * u;
+      if (e >= cols) break;
+      uint16_t h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (kBf16) {
+          const __nv_bfloat16 r = __float2bfloat16_rn(__fdiv_rn(bf16_round(v[u][i]), denom));
+          h[i] = *reinterpret_cast<const uint16_t*>(&r);
+        } else {
+          const __half r = __float2half_rn(__fdiv_rn(v[u][i], denom));
+          h[i] = *reinterpret_cast<const uint16_t*>(&r);
+        }
       }
-    }
-    if (vec) {
-      uint2 packed;
-      packed.x = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
-      packed.y = uint32_t(h[2]) | (uint32_t(h[3]) << 16);
-      __stcs(reinterpret_cast<uint2*>(dst + e), packed);
-    } else {
+      if (vec) {
+        uint2 packed;
+        packed.x = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
+        packed.y = uint32_t(h[2]) | (uint32_t(h[3]) << 16);
+        __stcs(reinterpret_cast<uint2*>(dst + e), packed);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (e + i < cols) dst[e + i] = h[i];
-    }
-    if (decay_rows) {
+        for (int i = 0; i < 4; ++i)
+          if (e + i < cols) dst[e + i] = h[i];
+      }
+      if (decay_rows) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = __fmul_rn(v[i], decay);
-      store4f(m, vec, e, cols, v);
+        for (int i = 0; i < 4; ++i) v[u][i] = __fmul_rn(v[u][i], decay);
+        store4f(m, vec, e, cols, v[u]);
+      }
     }
   }
   // Zero the padding columns so that they add nothing to any product.

@@ -124,6 +124,7 @@ apply_run_kernel(const WeightTable tab, long long first_row, long long total_row
   float* w = reinterpret_cast<float*>(tab.ptr[lo]) + (local - start) * cols;
   if (pos < 0) {
     if (vec) {
+#pragma unroll 4
       for (long long e = 4LL * lane; e < cols; e += 128) {
         float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
         v.x = __fmul_rn(v.x, decay_factor); v.y = __fmul_rn(v.y, decay_factor);
@@ -139,6 +140,7 @@ apply_run_kernel(const WeightTable tab, long long first_row, long long total_row
   const float d = denom[b * k + pos];
   const float sc = scale[b];
   if (vec) {
+#pragma unroll 4
     for (long long e = 4LL * lane; e < cols; e += 128) {
       float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
       const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(src + e));

@@ -41,15 +41,17 @@ from dionw_b200 import _matrix_step, _native, _workspace
 from dionw_b200._adamw import init_adamw_state
 from dionw_b200._buckets import Bucket, block_shape, build_buckets
 from dionw_b200._keys import (
-    ADAMW_STEP_STATE, EMA_SHADOW, EXP_AVG_SQ_STATE, EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_STATE, NUM_HEADS_KEY,
-    ROUTE_KEY, VARIANCE_STATE,
+    ADAMW_STEP_STATE, EMA_PENDING, EMA_SCRATCH_KEYS, EMA_SHADOW, EMA_STEP_COUNT_KEY, EXP_AVG_SQ_STATE,
+    EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_STATE, NUM_HEADS_KEY, ROUTE_KEY, VARIANCE_STATE,
 )
 from dionw_b200.ema import EMAConfig, IntegratedEMAOptimizer, ProfileRegion, no_profile
 from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate
-from dionw_b200.optimizer import _DionCore
+from dionw_b200.optimizer import _DionCore, _fill_legacy_keys, _require_same_structure
 from dionw_b200.routing import RouteKind
 
-__all__ = ["ShardedDion", "assign_by_cost", "newton_schulz_cost", "shard_range", "split_runs"]
+SHARD_KEY = "_dionw_shard"   # top-level entry of a per-rank checkpoint
+
+__all__ = ["SHARD_KEY", "ShardedDion", "assign_by_cost", "newton_schulz_cost", "shard_range", "split_runs"]
 
 # AdamW tensors at least this large are cut into per-rank element ranges.
 ADAMW_SHARD_MIN_ELEMENTS = 1 << 20
@@ -479,3 +481,82 @@ class ShardedDion(IntegratedEMAOptimizer, _ShardedCore):
             super()._swap_out(param, kept)
             return
         self._dist.all_gather_into_tensor(param.data.view(-1), kept, group=self._pg)
+
+    # ---- per-rank checkpoints -----------------------------------------------
+    def sharded_state_dict(self) -> dict[str, Any]:
+        """This rank's share of the state, as it is held: no collective, nothing gathered.
+
+        For sizes whose gathered ``state_dict()`` does not fit one GPU (the momentum of a
+        70B-shaped slice alone is 68 GB).  Every rank saves its own; ``load_sharded_state_dict``
+        takes it back on the same rank of a group of the same size with the same parameters.
+        """
+        helper = self._ema_helper
+        if helper is not None:
+            helper.flush_pending_updates()
+        self._ensure_shared()
+        packed = torch.optim.Optimizer.state_dict(self)
+        packed["state"] = {index: {k: v for k, v in entry.items() if k not in EMA_SCRATCH_KEYS}
+                           for index, entry in packed["state"].items()}
+        if helper is not None:
+            packed[EMA_STEP_COUNT_KEY] = helper.step_count
+        owners = self.owners()
+        packed[SHARD_KEY] = {
+            "rank": self._rank, "world": self._world,
+            "owners": [owners.get(p, -1) for group in self.param_groups for p in group["params"]],
+        }
+        return packed
+
+    def load_sharded_state_dict(self, state_dict: dict[str, Any]) -> None:
+        """Take back what ``sharded_state_dict`` of this rank saved.
+
+        Raises:
+            ValueError: If it is not a per-rank checkpoint, was saved by another rank or group
+                size, assigns the parameters differently, or differs in a structural key.
+        """
+        meta = state_dict.get(SHARD_KEY)
+        if not isinstance(meta, dict):
+            raise ValueError("not a per-rank checkpoint: use load_state_dict for the gathered layout")
+        if meta.get("rank") != self._rank or meta.get("world") != self._world:
+            raise ValueError(
+                f"per-rank checkpoint of rank {meta.get('rank')} of {meta.get('world')} "
+                f"cannot be loaded on rank {self._rank} of {self._world}")
+        saved_groups = _fill_legacy_keys(state_dict["param_groups"])
+        _require_same_structure(saved_groups, self.param_groups)
+        owners = self.owners()
+        if meta.get("owners") != [owners.get(p, -1) for group in self.param_groups for p in group["params"]]:
+            raise ValueError("per-rank checkpoint assigns the matrix parameters to other ranks")
+        helper = self._ema_helper
+        carries_ema = EMA_STEP_COUNT_KEY in state_dict
+        if carries_ema and helper is None:
+            raise ValueError("the per-rank checkpoint carries EMA shadows but this optimizer has no EMA")
+        if helper is not None:
+            helper.flush_pending_updates()
+            count = state_dict.get(EMA_STEP_COUNT_KEY)
+            if type(count) is not int or count < 0:
+                raise ValueError(f"per-rank checkpoint has no valid EMA step count ({count!r})")
+        on_gpu = helper is not None and helper.uses_gpu_shadow
+        pin = helper is not None and helper.config.pin_memory and not on_gpu
+        self.state.clear()
+        for saved, group in zip(saved_groups, self.param_groups, strict=True):
+            for key, value in saved.items():
+                if key != "params":
+                    group[key] = value
+            for index, param in zip(saved["params"], group["params"], strict=True):
+                source = state_dict["state"].get(index)
+                if source is None:
+                    continue
+                entry = self.state[param]
+                for key, value in source.items():
+                    if key == EMA_SHADOW:
+                        entry[key] = torch.empty_like(
+                            value, device=param.device if on_gpu else torch.device("cpu"), dtype=torch.float32,
+                            pin_memory=pin).copy_(value)
+                        entry[EMA_PENDING] = False
+                    elif isinstance(value, Tensor):
+                        entry[key] = value.to(param.device, copy=True)
+                    else:
+                        entry[key] = value
+        if helper is not None:
+            helper.step_count = state_dict[EMA_STEP_COUNT_KEY]
+        self._shared = None
+        self._buckets = None

@@ -38,3 +38,27 @@ def rel_l2(value: torch.Tensor, target: torch.Tensor) -> float:
     denom = float(target.norm())
     diff = float((value - target).norm())
     return diff if denom == 0.0 else diff / denom
+
+
+# Rounding error of the Gram iteration on prescribed spectra (256 x 1024, as the reference's
+# precision study does: bench/precision.py:31-117 there).  Its README lists, for an RTX 5090,
+# 0.003 (Gaussian), 0.037 / 0.039 (geometric decay over 4 / 6 decades) and 0.030 / 0.052
+# (rank 8 at 1, the rest at 1e-3 / 1e-4), other GPUs within 0.01.
+PUBLISHED_ROUNDING = {"gaussian": 0.003, "geometric4": 0.037, "geometric6": 0.039, "lowrank3": 0.030,
+                      "lowrank4": 0.052}
+
+
+def spectrum_matrix(name: str) -> torch.Tensor:
+    """A seeded ``[1, 256, 1024]`` fp32 matrix with the named singular values."""
+    rows, cols = 256, 1024
+    gen = torch.Generator().manual_seed(0)
+    if name == "gaussian":
+        return torch.randn(1, rows, cols, generator=gen)
+    left, _ = torch.linalg.qr(torch.randn(rows, rows, dtype=torch.float64, generator=gen))
+    right, _ = torch.linalg.qr(torch.randn(cols, rows, dtype=torch.float64, generator=gen))
+    if name.startswith("geometric"):
+        values = torch.logspace(0, -int(name[-1]), rows, dtype=torch.float64)
+    else:
+        values = torch.full((rows,), 10.0 ** -int(name[-1]), dtype=torch.float64)
+        values[:8] = 1.0
+    return ((left * values) @ right.mT).float()[None]

@@ -160,6 +160,33 @@ def _ema_worker(rank: int, world: int, port: int, failures, ema_device: str) -> 
             for key, value in entry.items():
                 if isinstance(value, torch.Tensor):
                     assert torch.equal(value, got["state"][index][key]), ("resumed", index, key)
+        # per-rank checkpoint: saved and loaded without any collective, through a file per rank
+        import io
+        import pytest as _pytest
+        from dionw_b200.distributed import SHARD_KEY
+        buffer = io.BytesIO()
+        torch.save(resumed.sharded_state_dict(), buffer)
+        buffer.seek(0)
+        mine = torch.load(buffer, weights_only=False)
+        assert mine[SHARD_KEY]["rank"] == rank and mine[SHARD_KEY]["world"] == world
+        again_net, again = build(ShardedDion)
+        again_net.load_state_dict(resumed_net.state_dict())
+        with _pytest.raises(ValueError, match="rank"):
+            again.load_sharded_state_dict({**mine, SHARD_KEY: {**mine[SHARD_KEY], "rank": 1 - rank}})
+        with _pytest.raises(ValueError, match="per-rank"):
+            again.load_sharded_state_dict(got)
+        again.load_sharded_state_dict(mine)
+        for net, opt in ((single_net, single), (again_net, again)):
+            _grads(net, 4)
+            opt.step()
+        for a, b in zip(single_net.parameters(), again_net.parameters()):
+            assert torch.equal(a, b), "weights after the per-rank resume differ"
+        want, got = single.state_dict(), again.state_dict()
+        assert want["_ema_step_count"] == got["_ema_step_count"] == 5
+        for index, entry in want["state"].items():
+            for key, value in entry.items():
+                if isinstance(value, torch.Tensor):
+                    assert torch.equal(value, got["state"][index][key]), ("per-rank resume", index, key)
         torch.cuda.synchronize()
     except Exception as exc:  # reported to the parent
         import traceback

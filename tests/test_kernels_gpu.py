@@ -7,7 +7,7 @@ import math
 import pytest
 import torch
 
-from conftest import load_golden, rel_l2
+from conftest import PUBLISHED_ROUNDING, load_golden, rel_l2, spectrum_matrix as _spectrum_matrix
 from oracle import dion_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -290,6 +290,42 @@ def test_mirrored_gram_products_stay_within_the_rounding_of_the_full_ones(native
     err_m = float((mirrored.double() @ mirrored.double().mT - eye).norm())
     err_f = float((full.double() @ full.double().mT - eye).norm())
     assert err_m < 1.2 * err_f + 0.05
+
+
+def _rounding_error(native, x: torch.Tensor, kind: int) -> float:
+    if kind == 0:
+        target = oracle.polynomial_fp64(x, oracle.GRAM_COEFFS, 1.0, eps=1e-7)
+    else:
+        target = oracle.polynomial_fp64(x, oracle.POLAR_EXPRESS_COEFFS, 1.02, eps=1e-7)
+    ours = _run_ns(native, x, kind).double()
+    return float((ours - target).norm() / target.norm())
+
+
+@pytest.mark.parametrize("name", sorted(PUBLISHED_ROUNDING))
+def test_gram_rounding_error_on_prescribed_spectra(native, name) -> None:
+    x = _spectrum_matrix(name)
+    ours = _rounding_error(native, x, 0)
+    cpu = oracle.gram_newton_schulz(x, eps=1e-7).double()
+    target = oracle.polynomial_fp64(x, oracle.GRAM_COEFFS, 1.0, eps=1e-7)
+    cpu_error = float((cpu - target).norm() / target.norm())
+    assert ours < PUBLISHED_ROUNDING[name] + 0.015, (ours, cpu_error)
+    assert ours < 1.3 * cpu_error + 3e-3, (ours, cpu_error)
+    if name != "gaussian":
+        # the restart keeps the error of ill-conditioned inputs small, below bf16 Polar Express
+        assert ours < 0.08
+        if name != "geometric2":
+            assert ours < _rounding_error(native, x, 1)
+
+
+@pytest.mark.parametrize("name", ["geometric4", "geometric6", "lowrank3", "lowrank4"])
+def test_fp32_input_beats_bf16_input_on_ill_conditioned_spectra(native, name) -> None:
+    """The step hands the iteration fp32 momentum rows; rounding them to bf16 first (as
+    microsoft/dion does) at least nearly doubles the error where singular values spread."""
+    x = _spectrum_matrix(name)
+    target = oracle.polynomial_fp64(x, oracle.GRAM_COEFFS, 1.0, eps=1e-7)
+    from_fp32 = _rounding_error(native, x, 0)
+    from_bf16 = float((_run_ns(native, x.bfloat16().float(), 0).double() - target).norm() / target.norm())
+    assert from_bf16 > 1.8 * from_fp32, (from_bf16, from_fp32)
 
 
 def _unit_bf16_batch(batch: int, m: int, n: int, seed: int) -> torch.Tensor:

@@ -9,7 +9,7 @@ from __future__ import annotations
 import pytest
 import torch
 
-from conftest import load_golden, rel_l2
+from conftest import PUBLISHED_ROUNDING, load_golden, rel_l2, spectrum_matrix
 from oracle import dion_oracle as oracle
 
 MATS = ("mats.0", "mats.1", "mats.2")
@@ -137,3 +137,20 @@ def test_row_scores_order_is_the_documented_one() -> None:
         w //= 2
         acc = acc[:w] + acc[w:2 * w]
     assert float(acc[0]) == float(s[0])
+
+
+@pytest.mark.parametrize("name", sorted(PUBLISHED_ROUNDING))
+def test_oracle_rounding_error_matches_the_published_table(name) -> None:
+    """Known answers: the reference publishes the rounding error of its Gram iteration (distance to
+    the fp64 polynomial) on five spectra.  The oracle, iterating in fp16 on the CPU, lands on them
+    (the Gaussian case uses another random matrix than the published one, hence the wider margin)."""
+    torch.set_num_threads(8)
+    x = spectrum_matrix(name)
+    target = oracle.polynomial_fp64(x, oracle.GRAM_COEFFS, 1.0, eps=1e-7)
+    error = rel_l2(oracle.gram_newton_schulz(x, eps=1e-7), target)
+    slack = 0.004 if name == "gaussian" else 0.003
+    assert abs(error - PUBLISHED_ROUNDING[name]) < slack, error
+    if name != "gaussian":
+        bf16_polar = oracle.quintic_bf16(x, 1e-7, oracle.POLAR_EXPRESS_COEFFS, 1.02)
+        polar_target = oracle.polynomial_fp64(x, oracle.POLAR_EXPRESS_COEFFS, 1.02, eps=1e-7)
+        assert error < 0.08 and error < rel_l2(bf16_polar, polar_target)
