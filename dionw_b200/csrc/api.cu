@@ -115,6 +115,18 @@ void run_job(dionw_cpu_ema_job* job) {
   }
   job->cv.notify_all();
   if (failure == 0) {
+    // A segment without a buffer is refused here, on the worker, so that the failure travels
+    // the same way a failed wait does: stored, both waits released, re-raised by the waiter.
+    for (size_t i = 0; i < job->numels.size(); ++i) {
+      if (job->numels[i] < 0 || (job->numels[i] > 0 && (job->shadows[i] == nullptr || job->staged[i] == nullptr))) {
+        failure = DIONW_ERR_WORKER;
+        snprintf(job->failure_text, sizeof(job->failure_text),
+                 "CPU EMA worker: segment %zu of %zu has no shadow or no staged buffer", i, job->numels.size());
+        break;
+      }
+    }
+  }
+  if (failure == 0) {
     // Split the flat element space of all segments evenly over the helper threads.
     int64_t total = 0;
     for (int64_t n : job->numels) total += n;

@@ -123,3 +123,54 @@ def test_checkpoint_structure_checks() -> None:
     muon = [_group(row_normalization="none", momentum_form="nesterov"), current[1]]
     with pytest.raises(ValueError, match="row_normalization"):
         _require_same_structure(filled, muon)
+
+
+# ---------------------------------------------------------------------------
+# the pinned-host EMA worker (no GPU involved: host tensors, no event)
+# ---------------------------------------------------------------------------
+def test_cpu_ema_job_lerps_host_segments() -> None:
+    from dionw_b200 import _native
+
+    gen = torch.Generator().manual_seed(3)
+    shadows = [torch.randn(n, generator=gen) for n in (1000, 7, 4096)]
+    staged = [torch.randn(n, generator=gen) for n in (1000, 7, 4096)]
+    expect = [s.clone() for s in shadows]
+    expect[0].lerp_(staged[0], 0.25)
+    expect[1].copy_(staged[1])          # first update of a shadow copies
+    expect[2].lerp_(staged[2], 0.25)
+    job = _native.CpuEmaJob(shadows, staged, [False, True, False], 0.25, None, 3)
+    job.wait_copy()
+    job.wait_update()
+    assert job.done()
+    job.close()
+    for got, want in zip(shadows, expect):
+        assert torch.equal(got, want)
+
+
+def test_cpu_ema_worker_failure_reaches_the_waiting_thread() -> None:
+    """Failure injected on the host: a segment whose staged buffer is missing.  The worker stores
+    the error and releases both waits; the tracker re-raises it as the reference does
+    (src/dionw/ema/_cpu_job.py:108-137, tracker.py:274-277)."""
+    from dionw_b200 import _native
+    from dionw_b200.ema.tracker import OptimizerIntegratedEMA
+
+    class Missing:
+        def data_ptr(self) -> int:
+            return 0
+
+        def numel(self) -> int:
+            return 16
+
+    shadow = torch.zeros(16)
+    job = _native.CpuEmaJob([shadow], [Missing()], [False], 0.5, None, 2)
+    with pytest.raises(RuntimeError, match="no shadow or no staged buffer"):
+        job.wait_update()
+    assert job.done()
+
+    tracker = OptimizerIntegratedEMA.__new__(OptimizerIntegratedEMA)
+    tracker._job = _native.CpuEmaJob([shadow], [Missing()], [False], 0.5, None, 2)
+    tracker._job_states = [{}]
+    with pytest.raises(RuntimeError, match="Asynchronous CPU EMA update failed"):
+        tracker._finish_job()
+    assert tracker._job is None
+    assert torch.equal(shadow, torch.zeros(16))
