@@ -214,7 +214,12 @@ class _ShardedCore(_DionCore):
                 if id(param) not in mine:   # a loaded checkpoint leaves full state everywhere: keep the owner's only
                     entry.pop(MOMENTUM_STATE, None)
                     entry.pop(VARIANCE_STATE, None)
-        self._shared = list(shared.values())
+        # Costliest buckets first: the gathers and weight updates of the large rounds then have the
+        # later rounds' work to hide behind, and the last gather of the step, which nothing
+        # hides, is the smallest.  Parameters are independent, so the order changes no result.
+        self._shared = sorted(
+            shared.values(),
+            key=lambda sb: -sum(newton_schulz_cost(sb.rows, sb.cols, sb.k, b) for b in sb.blocks))
         self._buckets = [sb.local for sb in self._shared if sb.local is not None]
         return self._shared
 
