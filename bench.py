@@ -371,6 +371,15 @@ def run_gpu_arm(args) -> None:
         dist.init_process_group("nccl", device_id=device)
     _native.library()
 
+    layers, d, dkv, dff, vocab = CONFIGS[args.config]
+    weights_bytes = 4.0 * (layers * (2 * d * d + 2 * d * dkv + 3 * d * dff)
+                           + vocab * d * (1 if args.config in EMBED_ONLY_WITH_EMA else 2))
+    # replicated weights + this rank's share of momentum (+ EMA shadows) + scratch must fit beside the gradients
+    need = weights_bytes * (1.0 + (1.0 + (1.0 if args.config in EMBED_ONLY_WITH_EMA else 0.0)) / world) + 16e9
+    have = torch.cuda.get_device_properties(device).total_memory
+    if need > have:
+        raise SystemExit(f"bench.py: config {args.config} needs about {need / 1e9:.0f} GB per GPU on {world} GPU(s), "
+                         f"this GPU has {have / 1e9:.0f} GB: run it on more GPUs")
     model = LlamaShaped(args.config, device)
     model.init_(seed=0)
     routes = {} if model.lm_head is None else {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}

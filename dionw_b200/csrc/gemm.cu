@@ -111,14 +111,6 @@ int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, 
   attribute.val.clusterDim.z = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  static bool reported = false;
-  if (!reported && std::getenv("DIONW_GEMM_DEBUG") != nullptr) {
-    reported = true;
-    int clusters = -1;
-    cudaError_t err = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
-    fprintf(stderr, "[dionw] gemm2: max active clusters of 2 = %d (%s), pairs launched = %d, SMs = %d\n", clusters,
-            cudaGetErrorString(err), pairs, sm_count());
-  }
   count_launch();
   return check_cuda(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p), "gemm2_kernel launch");
 }
