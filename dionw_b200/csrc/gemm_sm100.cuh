@@ -100,20 +100,21 @@ __device__ __forceinline__ uint64_t global_ns() {
 // the rest of the CTA to stop through `abort_flag`.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t start = global_ns();
   uint32_t spins = 0;
-  while (true) {
-    if (mbar_try(bar, parity)) return true;
+  uint64_t start = 0;   // the timer is first read after 1024 failed tries: a wait that ends soon never pays for it
+  while (!mbar_try(bar, parity)) {
     if ((++spins & 1023u) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_ns() - start > 2000000000ull) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) {
         *abort_flag = 1;
         atomicExch(status, kWaitCode);
         return false;
       }
     }
   }
+  return true;
 }
 
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
