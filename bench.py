@@ -20,6 +20,7 @@ from __future__ import annotations
 import argparse
 import contextlib
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -43,6 +44,8 @@ CONFIGS = {
     # 20-layer slice of the Llama-3-70B shapes, embedding only, GPU EMA (decay 0.9999): 8 GPUs
     "llama3-70b-20layers": (20, 8192, 1024, 28672, 128256),
     "llama3-70b-1layer": (1, 8192, 1024, 28672, 16032),
+    # GPT-2-small (12 layers, d = 768, ~124 M parameters): the shapes are fixed in Gpt2Shaped
+    "gpt2-small": (12, 768, 768, 3072, 50257),
 }
 EMBED_ONLY_WITH_EMA = {"llama3-70b-20layers", "llama3-70b-1layer"}
 # Above this many bytes of fp32 weights + gradients per GPU the gradients are one tensor per
@@ -81,6 +84,31 @@ class LlamaShaped(nn.Module):
             p.normal_(0.0, 0.02, generator=gen)
 
 
+class Gpt2Block(nn.Module):
+    def __init__(self, d: int, device) -> None:
+        super().__init__()
+        mk = lambda *shape: nn.Parameter(torch.empty(*shape, device=device))  # noqa: E731
+        self.ln1_w, self.ln1_b, self.ln2_w, self.ln2_b = mk(d), mk(d), mk(d), mk(d)
+        self.c_attn, self.c_proj = mk(d, 3 * d), mk(d, d)
+        self.fc, self.proj = mk(d, 4 * d), mk(4 * d, d)
+
+
+class Gpt2Shaped(nn.Module):
+    """GPT-2-small's parameter shapes (12 layers, d = 768): every matrix has a dimension below 1024,
+    so all rows are updated (no selection); wte and wpe go through AdamW."""
+
+    def __init__(self, device) -> None:
+        super().__init__()
+        self.wte = nn.Embedding(50257, 768, device=device)
+        self.wpe = nn.Embedding(1024, 768, device=device)
+        self.layers = nn.ModuleList(Gpt2Block(768, device) for _ in range(12))
+        self.norm = nn.Parameter(torch.empty(768, device=device))
+        self.ln_f_b = nn.Parameter(torch.empty(768, device=device))
+        self.lm_head = None
+
+    init_ = LlamaShaped.init_
+
+
 def flops_newton_schulz(m: int, n: int) -> float:
     """Algorithmic FLOPs of one orthogonalization of an m x n operand (m <= n): the Gram
     schedule's product census, symmetric products counted as half."""
@@ -100,26 +128,45 @@ def traffic_newton_schulz(m: int, n: int) -> float:
     return NS_TRAFFIC_CALIBRATION * 2.0 * (6.0 * m * n + 40.0 * m * m)
 
 
-def census(model: LlamaShaped, fraction: float = 0.25, min_dim: int = 1024) -> dict[str, float]:
-    """Algorithmic work of one step: elements, bytes per pass, Newton-Schulz FLOPs."""
-    e = es = ns = adam = ns_traffic = 0.0
-    for layer in model.layers:
-        for w in (layer.q, layer.k, layer.v, layer.o, layer.gate, layer.up, layer.down):
-            rows, cols = w.shape
-            k = -(-int(fraction * rows * 1e9) // int(1e9)) if min(rows, cols) >= min_dim else rows
-            k = min(rows, max(k, 1))
+def flops_newton_schulz_executed(m: int, n: int) -> float:
+    """FLOPs the kernels execute for the same orthogonalization: the products Q Z, G Z and Z RZ are
+    symmetric too and run on the lower-triangle schedule (7 m^3 instead of 11.5 m^3)."""
+    if m == n:
+        return 2.0 * 10.0 * m**3
+    return 2.0 * (3.0 * m * m * n + 7.0 * m**3)
+
+
+def census(groups: list[dict]) -> dict[str, float]:
+    """Algorithmic work of one step, from the optimizer's groups: elements, bytes per pass,
+    Newton-Schulz FLOPs.  Blocks that update every row (fraction 1) take the full-row path:
+    accumulate, copy and decay in one pass (16 B/element: read G and M, write M and the fp32 copy),
+    then norm + pack (6 B/element)."""
+    from dionw_b200._keys import FRACTION_KEY, ROUTE_KEY
+    from dionw_b200.routing import RouteKind
+
+    e = es = ns = adam = ns_traffic = ns_exec = full = 0.0
+    for group in groups:
+        if RouteKind(group[ROUTE_KEY]) is not RouteKind.MATRIX:
+            adam += sum(p.numel() for p in group["params"])
+            continue
+        fraction = float(group[FRACTION_KEY])
+        for w in group["params"]:
+            rows, cols = w.shape[0], w[0].numel()
+            k = min(rows, max(1, math.ceil(fraction * rows)))
             e += rows * cols
             es += k * cols
-            ns += flops_newton_schulz(min(k, cols), max(k, cols))
-            ns_traffic += traffic_newton_schulz(min(k, cols), max(k, cols))
-    for p in model.parameters():
-        adam += p.numel()
-    adam -= e
+            if k == rows:
+                full += rows * cols
+            m, n = min(k, cols), max(k, cols)
+            ns += flops_newton_schulz(m, n)
+            ns_traffic += traffic_newton_schulz(m, n)
+            ns_exec += flops_newton_schulz_executed(m, n)
+    selecting = e - full
     return {
         "matrix_elements": e, "selected_elements": es, "adamw_elements": adam, "ns_flops": ns,
-        "ns_traffic": ns_traffic,
-        "bytes_accumulate": 12 * e, "bytes_pack": 10 * es, "bytes_finish": 2 * es,
-        "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam, "bytes_ema": 12 * (e + adam),
+        "ns_traffic": ns_traffic, "ns_flops_executed": ns_exec,
+        "bytes_accumulate": 12 * selecting + 16 * full, "bytes_pack": 10 * (es - full) + 10 * full,
+        "bytes_finish": 2 * es, "bytes_apply": 8 * e + 2 * es, "bytes_adamw": 28 * adam, "bytes_ema": 12 * (e + adam),
     }
 
 
@@ -214,7 +261,14 @@ def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     gen = torch.Generator().manual_seed(0)
-    shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
+    if config == "gpt2-small":
+        shapes = [(d, 3 * d), (d, d), (d, 4 * d), (4 * d, d)]       # one whole layer
+        per_layer = shapes
+        what = f"one layer's c_attn, c_proj, fc, proj blocks + one LayerNorm weight[{d}]"
+    else:
+        shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
+        per_layer = [(d, d)] * 2 + [(dkv, d)] * 2 + [(dff, d)] * 2 + [(d, dff)]
+        what = f"one layer's q, o ({d}x{d}) and k, v ({dkv}x{d}) blocks + one RMSNorm[{d}]"
     weights = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
     norm = torch.randn(d, generator=gen) * 0.02
     grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
@@ -227,18 +281,19 @@ def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
         opt.step(grads, [gnorm])
         if i >= warmup:
             times.append((time.perf_counter() - t0) * 1e3)
-    sample_flops = sum(flops_newton_schulz(*sorted((min(r, -(-r // 4) if min(r, c) >= 1024 else r), c)))
-                       for r, c in shapes)
-    model_flops = 0.0
-    for r, c in [(d, d)] * 2 + [(dkv, d)] * 2 + [(dff, d)] * 2 + [(d, dff)]:
+
+    def block_flops(r: int, c: int) -> float:
         k = -(-r // 4) if min(r, c) >= 1024 else r
-        model_flops += layers * flops_newton_schulz(min(k, c), max(k, c))
+        return flops_newton_schulz(min(k, c), max(k, c))
+
+    sample_flops = sum(block_flops(r, c) for r, c in shapes)
+    model_flops = layers * sum(block_flops(r, c) for r, c in per_layer)
     per_step = statistics.median(times)
     scaled = per_step * model_flops / sample_flops
     return {
         "value": scaled, "unit": "ms", "cores": cores, "kind": "port",
-        "sample": (f"CPU oracle (torch eager, {cores} threads) on one layer's q, o ({d}x{d}) and k, v ({dkv}x{d}) "
-                   f"blocks + one RMSNorm[{d}]: median {per_step:.1f} ms per sample step over {steps} steps, "
+        "sample": (f"CPU oracle (torch eager, {cores} threads) on {what}: "
+                   f"median {per_step:.1f} ms per sample step over {steps} steps, "
                    f"scaled by Newton-Schulz FLOPs x{model_flops / sample_flops:.0f} to the whole set"),
         "sample_ms": per_step,
     }
@@ -380,7 +435,7 @@ def run_gpu_arm(args) -> None:
     if need > have:
         raise SystemExit(f"bench.py: config {args.config} needs about {need / 1e9:.0f} GB per GPU on {world} GPU(s), "
                          f"this GPU has {have / 1e9:.0f} GB: run it on more GPUs")
-    model = LlamaShaped(args.config, device)
+    model = Gpt2Shaped(device) if args.config == "gpt2-small" else LlamaShaped(args.config, device)
     model.init_(seed=0)
     routes = {} if model.lm_head is None else {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
     groups, _ = dionw.param_groups(model, routes=routes)
@@ -410,7 +465,7 @@ def run_gpu_arm(args) -> None:
             p.grad = by_shape[tuple(p.shape)]
         else:
             p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
-    work = census(model)
+    work = census(groups)
 
     def barrier() -> None:
         if distributed:
@@ -558,6 +613,10 @@ def run_gpu_arm(args) -> None:
                              "3584x4096 blocks and scaled by blocks (traffic grows with the blocks processed)"),
             "peak_kind": f"{peaks_kind} bf16 cuBLAS, sustained (the kernel is timed inside the step)",
             "flops_per_step": work["ns_flops"] * share,
+            "executed": {"TFLOP/s": work["ns_flops_executed"] * share / ns_ms / 1e9 if ns_ms else None,
+                         "frac": work["ns_flops_executed"] * share / ns_ms / 1e9 / peak_tf if ns_ms else None,
+                         "note": "achieved counts the algorithmic census 2(3m^2n + 11.5m^3) per block; the kernels "
+                                 "execute 2(3m^2n + 7m^3) because three more products per iteration are mirrored"},
         },
         "stages": stage_report,
         "cpu_baseline": cpu,

@@ -357,24 +357,26 @@ def test_microbenchmark_batches_match_oracle_through_the_public_entry(native, m,
     assert max(our_err) < 1.2 * max(ref_err) + 0.05
 
 
-def test_microbenchmark_large_shape_reaches_the_small_shapes_orthogonality(native) -> None:
-    """4096 x 14336 (the oracle would take minutes): the error per sqrt(rows) is a property of
-    the five fixed polynomial steps and the aspect ratio, not of the size, so it must stay at
-    the level the 1024 x 3584 case (same aspect ratio) reaches on the oracle."""
+@pytest.mark.parametrize("m,n,small_m,small_n", [(4096, 14336, 1024, 3584), (7168, 8192, 896, 1024)])
+def test_large_operands_reach_the_orthogonality_of_small_ones(native, m, n, small_m, small_n) -> None:
+    """4096 x 14336 (microbenchmark) and 7168 x 8192 (the gate/up operand of the 70B-shaped slice): the
+    oracle would take minutes, but the error per sqrt(rows) is a property of the five fixed polynomial
+    steps and the aspect ratio, not of the size, so it must stay at the level a small operand of the same
+    aspect ratio reaches on the oracle."""
     from dionw_b200.newton_schulz import gram_polar_express
 
-    small = _unit_bf16_batch(1, 1024, 3584, seed=5)
+    small = _unit_bf16_batch(1, small_m, small_n, seed=5)
     torch.set_num_threads(8)
     expect = oracle.gram_newton_schulz(small.float()).double()[0]
-    level = float((expect @ expect.T - torch.eye(1024, dtype=torch.float64)).norm()) / 1024**0.5
+    level = float((expect @ expect.T - torch.eye(small_m, dtype=torch.float64)).norm()) / small_m**0.5
     gen = torch.Generator(device=DEV).manual_seed(11)
-    big = torch.randn(2, 4096, 14336, device=DEV, generator=gen)
+    big = torch.randn(2, m, n, device=DEV, generator=gen)
     big = (big / torch.linalg.matrix_norm(big, keepdim=True)).bfloat16()
     y = gram_polar_express(big, 1e-8).float()
     assert native.device_status() == 0
-    eye = torch.eye(4096, device=DEV)
+    eye = torch.eye(m, device=DEV)
     for i in range(2):
-        err = float(torch.linalg.matrix_norm(y[i] @ y[i].T - eye)) / 4096**0.5
+        err = float(torch.linalg.matrix_norm(y[i] @ y[i].T - eye)) / m**0.5
         assert err < 1.25 * level + 0.01, (err, level)
 
 
