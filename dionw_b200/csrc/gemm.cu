@@ -74,11 +74,12 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Param
   return launch_status("gemm_kernel launch");
 }
 
-// Two-CTA tiles (clusters of two CTAs): on when the environment asks for it.
+// Two-CTA tiles (clusters of two CTAs) unless the environment says DIONW_GEMM_CTA_PAIRS=0,
+// which selects the one-CTA kernel.
 bool use_cta_pairs() {
   static const bool on = [] {
     const char* v = std::getenv("DIONW_GEMM_CTA_PAIRS");
-    return v != nullptr && v[0] == '1';
+    return v == nullptr || v[0] != '0';
   }();
   return on;
 }

@@ -1,7 +1,8 @@
-"""The two-CTA (cta_group::2) variant of the tcgen05 GEMM, switched on with
-DIONW_GEMM_CTA_PAIRS=1.  The switch is read once per process, so the check runs in a
-child process and compares the products with fp32 torch matmuls, and the Newton-Schulz
-built on them with the one-CTA kernel of this process.
+"""The one-CTA variant of the tcgen05 GEMM, selected with DIONW_GEMM_CTA_PAIRS=0 (the
+default is the two-CTA, cta_group::2 kernel, which every other test runs on).  The switch
+is read once per process, so the check runs in a child process and compares the products
+with fp32 torch matmuls, and the Newton-Schulz built on them with the two-CTA kernel of
+this process.
 """
 import os
 import subprocess
@@ -53,7 +54,7 @@ for blocks, m, k in [(2, 768, 1024), (1, 304, 520), (4, 256, 512)]:
     nat.symmetric_product(g, r, b=z, cin=g, beta=0.5)
     worst = max(worst, rel(r, g.float() @ z.float() + 0.5 * g.float()))
     assert torch.equal(r, r.transpose(1, 2))
-# the Gram Newton-Schulz on the pair kernel; the parent compares it with its own
+# the Gram Newton-Schulz on this kernel; the parent compares it with its own
 x = (torch.randn(6, 256, 1024, device=dev, generator=torch.Generator(dev).manual_seed(3)) / 512).half()
 ws = torch.empty(nat.newton_schulz_workspace_bytes(6, 256, 1024, 0), dtype=torch.uint8, device=dev)
 o = torch.empty(6, 256, 1024, dtype=torch.bfloat16, device=dev)
@@ -65,11 +66,11 @@ print("WORST", worst)
 """
 
 
-def test_two_cta_gemm_in_child_process(tmp_path):
+def test_one_cta_gemm_in_child_process(tmp_path):
     from dionw_b200 import _native as nat
 
-    out_file = tmp_path / "ns_pairs.pt"
-    env = dict(os.environ, DIONW_GEMM_CTA_PAIRS="1", PYTHONPATH=ROOT)
+    out_file = tmp_path / "ns_one_cta.pt"
+    env = dict(os.environ, DIONW_GEMM_CTA_PAIRS="0", PYTHONPATH=ROOT)
     done = subprocess.run([sys.executable, "-c", CHILD, str(out_file)], env=env, capture_output=True, text=True,
                           timeout=600, cwd=ROOT)
     assert done.returncode == 0, done.stdout + done.stderr
