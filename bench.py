@@ -519,9 +519,11 @@ def run_gpu_arm(args) -> None:
     timer.enabled = True
     stage_steps = max(1, min(3, args.steps))
     for _ in range(stage_steps):
-        optimizer.step()
+        with timer("whole_step"):
+            optimizer.step()
     stages = {k: v / stage_steps for k, v in timer.collect().items()}
     timer.enabled = False
+    whole_ms = stages.pop("whole_step", None)   # the same steps, bracketed once: shows what lies between the stages
 
     # ---- host dispatch: wall time for step() to return with the GPU idle at the start and
     # no synchronize inside (one step's launches fit the driver's launch queue)
@@ -588,6 +590,7 @@ def run_gpu_arm(args) -> None:
         "apply": {"ms": stages.get("apply"), "GB/s": gbs("bytes_apply", "apply")},
         "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
         "hbm_peak_GB/s": peaks["hbm_gbs"],
+        "between_stages_ms": (whole_ms - sum(v for v in stages.values())) if whole_ms is not None else None,
     }
     if "ema" in stages:
         stage_report["ema"] = {"ms": stages["ema"], "GB/s": gbs("bytes_ema", "ema", share)}

@@ -59,6 +59,17 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int64_t inner, int64
   return DIONW_OK;
 }
 
+// Products are launched with programmatic stream serialization (the kernels wait with
+// griddepcontrol.wait before they touch global memory), unless DIONW_GEMM_PDL=0.  Measured on the
+// Llama-3-8B-shaped step: 95.1-96.2 ms with it, 98.3-99.0 ms without (about 290 product launches per step).
+bool use_dependent_launch() {
+  static const bool on = [] {
+    const char* v = std::getenv("DIONW_GEMM_PDL");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
 template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Params& p, cudaStream_t stream) {
   auto kernel = gemm::gemm_kernel<InT, OutT, kBMajorMN, kSym>;
@@ -70,8 +81,18 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Param
   const int total = p.tiles_per_batch * p.batches;
   if (total == 0) return DIONW_OK;
   const int grid = total < sm_count() ? total : sm_count();
-  kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(map_a, map_b, p);
-  return launch_status("gemm_kernel launch");
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(unsigned(grid));
+  config.blockDim = dim3(gemm::kThreads);
+  config.dynamicSmemBytes = gemm::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = use_dependent_launch() ? 1 : 0;
+  count_launch();
+  return check_cuda(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p), "gemm_kernel launch");
 }
 
 // Two-CTA tiles (clusters of two CTAs) unless the environment says DIONW_GEMM_CTA_PAIRS=0,
@@ -105,13 +126,15 @@ int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, 
   config.blockDim = dim3(gemm2::kThreads);
   config.dynamicSmemBytes = gemm2::kSmemBytes;
   config.stream = stream;
-  cudaLaunchAttribute attribute;
-  attribute.id = cudaLaunchAttributeClusterDimension;
-  attribute.val.clusterDim.x = 2;
-  attribute.val.clusterDim.y = 1;
-  attribute.val.clusterDim.z = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 2;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = use_dependent_launch() ? 2 : 1;
   count_launch();
   return check_cuda(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p), "gemm2_kernel launch");
 }

@@ -197,6 +197,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   cluster_sync();   // both CTAs' barriers exist before anyone arrives on a peer's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  gemm::griddep_wait();     // set-up above overlaps the tail of the previous product; global memory from here on
+  gemm::griddep_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)

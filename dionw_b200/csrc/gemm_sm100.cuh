@@ -90,6 +90,14 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Programmatic dependent launch: the host launches every product with the stream-serialization
+// attribute, so the CTAs of the next product may become resident, and run their set-up, as soon as
+// CTAs of this one exit.  Nothing of global memory is read or written before griddep_wait()
+// returns, which it does once the previous kernel of the stream has completed and its writes are
+// visible; griddep_launch() then allows the kernel after this one to start the same way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -472,6 +480,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();
+  griddep_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
