@@ -118,10 +118,10 @@ def flops_newton_schulz(m: int, n: int) -> float:
 
 
 # DRAM bytes the products of one Gram Newton-Schulz move for an m x n operand: the operand census
-# 2 B x (6 m n + 40 m^2) (every product reads its operands and writes its result once) times 1.03,
+# 2 B x (6 m n + 40 m^2) (every product reads its operands and writes its result once) times 1.06,
 # the ratio an ncu capture of the 18 products of four 3584 x 4096 blocks measured against it
-# (1.240 GB per block; dram__bytes_read.sum + dram__bytes_write.sum).
-NS_TRAFFIC_CALIBRATION = 1.03
+# (1.278 GB per block; dram__bytes_read.sum + dram__bytes_write.sum).
+NS_TRAFFIC_CALIBRATION = 1.06
 
 
 def traffic_newton_schulz(m: int, n: int) -> float:
@@ -398,7 +398,7 @@ def run_ns_microbench(args) -> None:
         "dtype": "fp16 iteration, fp32 accumulate, bf16 result", "data": "synthetic",
         "config": {"workload": "Gram Newton-Schulz, batches of 16 at 1024x1024, 1024x4096, 4096x14336, 8192x28672",
                    "l2": "operands of the two large shapes exceed L2; medians of per-call CUDA-event times"},
-        "roofline": {"kernel": f"gemm_kernel (products of the {big['shape'][0]}x{big['shape'][1]} batch)",
+        "roofline": {"kernel": f"gemm2_kernel (products of the {big['shape'][0]}x{big['shape'][1]} batch)",
                      "bound": "tensor", "achieved": big["TFLOP/s"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": big["TFLOP/s"] / peaks["bf16_tflops"], "traffic": None,
                      "peak_kind": f"{peaks_kind} bf16 cuBLAS, burst (each batch is timed alone)"},
@@ -608,11 +608,11 @@ def run_gpu_arm(args) -> None:
                    "gradients": ("one tensor per shape shared by all layers (weights + gradients would not fit "
                                  "beside the state)" if shared_grads else "one tensor per parameter")},
         "roofline": {
-            "kernel": "gemm_kernel (all Newton-Schulz products of a step)",
+            "kernel": "gemm2_kernel (all Newton-Schulz products of a step)",
             "bound": "tensor", "achieved": ns_tflops, "peak": peak_tf, "unit": "TFLOP/s",
             "frac": ns_tflops / peak_tf if ns_tflops else None, "traffic": work["ns_traffic"] * share,
-            "traffic_kind": ("DRAM bytes of all gemm_kernel launches of one step on this rank: the operand census "
-                             "of the products, calibrated x1.03 on an ncu capture of the 18 products of four "
+            "traffic_kind": ("DRAM bytes of all gemm2_kernel launches of one step on this rank: the operand census "
+                             "of the products, calibrated x1.06 on an ncu capture of the 18 products of four "
                              "3584x4096 blocks and scaled by blocks (traffic grows with the blocks processed)"),
             "peak_kind": f"{peaks_kind} bf16 cuBLAS, sustained (the kernel is timed inside the step)",
             "flops_per_step": work["ns_flops"] * share,
