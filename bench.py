@@ -408,6 +408,64 @@ def run_ns_microbench(args) -> None:
 
 
 # ---------------------------------------------------------------------------
+# sustained plain GEMM against cuBLAS (``--config gemm-sustained``)
+# ---------------------------------------------------------------------------
+def run_gemm_sustained(args) -> None:
+    """One 8192^3 bf16 product (A B^T) looped for about four seconds, under the board's power cap:
+    torch.matmul (cuBLAS) first, then this library's ``dionw_batched_gemm`` on the same operands,
+    with the SM clock and the power sampled every 100 ms.  Says how much of cuBLAS's sustained
+    rate the tcgen05 main loop reaches at equal power (the epilogue is 1/128 of the work here)."""
+    from dionw_b200 import _native
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    _native.library()
+    n = 8192
+    gen = torch.Generator(device=device).manual_seed(0)
+    a = (torch.randn(1, n, n, device=device, generator=gen) / n**0.5).bfloat16()
+    b = torch.randn(1, n, n, device=device, generator=gen).bfloat16()
+    out = torch.empty(1, n, n, dtype=torch.bfloat16, device=device)
+    arms = {"cublas": lambda: torch.matmul(a[0], b[0].T, out=out[0]),
+            "dionw_b200": lambda: _native.batched_gemm(a, b, out, b_is_nk=True)}
+    seconds = 4.0
+    results = {}
+    launches_before = _native.launch_count()
+    for name, call in arms.items():
+        for _ in range(max(3, args.warmup)):
+            call()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count, t0 = 0, time.time()
+        start.record()
+        while time.time() - t0 < seconds:
+            for _ in range(20):
+                call()
+            count += 20
+            torch.cuda.synchronize()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        results[name] = {"TFLOP/s": 2.0 * n**3 * count / ms / 1e9, "products": count, "seconds": ms / 1e3,
+                         "clocks": sampler.stop()}
+    ours, theirs = results["dionw_b200"]["TFLOP/s"], results["cublas"]["TFLOP/s"]
+    line = {
+        "metric": "sustained_gemm_tflops", "value": ours, "unit": "TFLOP/s", "n_gpus": 1, "steps": results["dionw_b200"]["products"],
+        "warmup": max(3, args.warmup), "ms_per_step": 1e3 * results["dionw_b200"]["seconds"] / results["dionw_b200"]["products"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16, fp32 accumulate",
+        "data": "synthetic", "config": {"workload": "8192^3 bf16 A B^T looped for 4 s", "l2": "operands (268 MB) exceed L2"},
+        "roofline": {"kernel": "gemm2_kernel" if os.environ.get("DIONW_GEMM_CTA_PAIRS", "1") != "0" else "gemm_kernel",
+                     "bound": "tensor", "achieved": ours, "peak": theirs, "unit": "TFLOP/s", "frac": ours / theirs,
+                     "traffic": None, "peak_kind": "torch.matmul (cuBLAS) on the same operands, same call, same power cap"},
+        "arms": results, "gpu_launches": _native.launch_count() - launches_before,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
 # the GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu_arm(args) -> None:
@@ -640,18 +698,20 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
-    parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns"], default="llama3-8b")
+    parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     parser.add_argument("--overlap-apply", action="store_true",
                         help="sharded step: weight update of a round on a side stream beside the next round")
     args = parser.parse_args()
-    if args.config == "gram-ns":
+    if args.config in ("gram-ns", "gemm-sustained"):
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "the gram-ns microbenchmark has no CPU arm"}))
-        else:
+            print(json.dumps({"impl": "reference", "unavailable": f"the {args.config} microbenchmark has no CPU arm"}))
+        elif args.config == "gram-ns":
             run_ns_microbench(args)
+        else:
+            run_gemm_sustained(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
