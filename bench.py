@@ -220,6 +220,14 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def samples(self) -> int:
+        if self.proc is None or self.file is None:
+            return 1 << 30
+        try:
+            return Path(self.file.name).read_text().count("\n")
+        except OSError:
+            return 1 << 30
+
     def stop(self) -> dict | None:
         if self.proc is None:
             return None
@@ -317,6 +325,127 @@ def run_reference_arm(args) -> None:
 
 
 # ---------------------------------------------------------------------------
+# the reference's own GPU step (``--impl reference-gpu``; not the driver's reference arm)
+# ---------------------------------------------------------------------------
+def run_reference_gpu_arm(args) -> None:
+    """The UNMODIFIED reference package, if a copy sits under ``baseline/_ref`` (git-ignored), on the
+    same workload through its own public API: ``dionw.param_groups`` + ``dionw.Dion(...).step()``
+    (torch.compile + Triton + cuBLAS inside).  Timed like the B200 arm.  Prints an ``unavailable``
+    line when the package is not there or does not run under this torch."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_root = ROOT / "baseline" / "_ref"
+
+    def unavailable(why: str) -> None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": why[:400]}), flush=True)
+
+    if not (ref_root / "dionw" / "__init__.py").exists():
+        unavailable("no reference package under baseline/_ref (its build backend, hatchling, is not installable offline)")
+        return
+    sys.path.insert(0, str(ref_root))
+    try:
+        import dionw as reference
+    except Exception as exc:  # noqa: BLE001 - the reason is the result
+        unavailable(f"import failed: {exc!r}")
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    try:
+        model = Gpt2Shaped(device) if args.config == "gpt2-small" else LlamaShaped(args.config, device)
+        model.init_(seed=0)
+        routes = {} if model.lm_head is None else {model.lm_head.weight: reference.Route(reference.RouteKind.ADAMW)}
+        groups, _ = reference.param_groups(model, routes=routes)
+        optimizer = reference.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+        gen = torch.Generator(device=device).manual_seed(1)
+        for p in model.parameters():
+            p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
+        t0 = time.time()
+        for _ in range(max(3, args.warmup)):
+            optimizer.step()
+        torch.cuda.synchronize()
+        warm_s = time.time() - t0
+        sampler = ClockSampler(0)
+        sampler.start()
+        times = []
+        for _ in range(args.steps):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            optimizer.step()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+        clocks = sampler.stop()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        unavailable(f"the reference's step failed under torch {torch.__version__}: {exc!r} | {traceback.format_exc()[-300:]}")
+        return
+    total = sum(times)
+    line = {
+        "impl": "reference-gpu", "metric": "optimizer_step_ms", "value": total / len(times), "unit": "ms", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total / len(times),
+        "median_ms": statistics.median(times), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp32 state, fp16 Newton-Schulz", "data": "synthetic",
+        "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
+                   "arm": f"unmodified reference package (torch {torch.__version__}, its Triton + cuBLAS step), "
+                          f"warm-up incl. compilation {warm_s:.1f} s"},
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu_ns(args) -> None:
+    """The reference's own Gram Newton-Schulz entry on the microbenchmark's batches (same inputs as
+    ``--config gram-ns``), whole-call device time, median."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "dionw" / "__init__.py").exists():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "no reference package under baseline/_ref"}))
+        return
+    sys.path.insert(0, str(ref_root))
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    rows_out = []
+    try:
+        from dionw.newton_schulz import NewtonSchulz, newton_schulz_fn
+
+        fn = newton_schulz_fn(NewtonSchulz.GRAM)
+        for m, n in NS_SHAPES:
+            gen = torch.Generator(device=device).manual_seed(m * 31 + n)
+            x = torch.randn(NS_BATCH, m, n, device=device, generator=gen)
+            x = (x / torch.linalg.matrix_norm(x, keepdim=True)).bfloat16()
+            for _ in range(max(3, args.warmup)):
+                y = fn(x, 1e-8)
+            times = []
+            for _ in range(args.steps):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                y = fn(x, 1e-8)
+                end.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(end))
+            call_ms = statistics.median(times)
+            y0 = y[0].float()
+            err = float(torch.linalg.matrix_norm(y0 @ y0.T - torch.eye(m, device=device)))
+            rows_out.append({"shape": [m, n], "batch": NS_BATCH, "call_ms": call_ms,
+                             "TFLOP/s_of_call": NS_BATCH * flops_newton_schulz(m, n) / call_ms / 1e9,
+                             "orthogonality_error": err, "error_per_sqrt_m": err / m**0.5})
+            del x, y, y0
+            torch.cuda.empty_cache()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"failed under torch {torch.__version__}: {exc!r} | "
+                          f"{traceback.format_exc()[-300:]}", "shapes": rows_out}), flush=True)
+        return
+    print(json.dumps({"impl": "reference-gpu", "metric": "gram_newton_schulz_tflops", "unit": "TFLOP/s",
+                      "value": sum(NS_BATCH * flops_newton_schulz(*r["shape"]) for r in rows_out)
+                      / sum(r["call_ms"] for r in rows_out) / 1e9,
+                      "config": {"workload": "the reference's Gram Newton-Schulz entry, whole call"}, "shapes": rows_out}),
+          flush=True)
+
+
+# ---------------------------------------------------------------------------
 # the Gram Newton-Schulz microbenchmark (``--config gram-ns``)
 # ---------------------------------------------------------------------------
 NS_SHAPES = ((1024, 1024), (1024, 4096), (4096, 14336), (8192, 28672))
@@ -387,6 +516,17 @@ def run_ns_microbench(args) -> None:
         del x, packed, scratch, work, y
         torch.cuda.empty_cache()
     launches = _native.launch_count() - launches_before
+    extra_deadline = time.time() + 4.0
+    while True:
+        need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
+        if distributed:   # every rank takes the same number of extra steps: rank 0 decides
+            flag = torch.tensor([1.0 if need else 0.0], device=device)
+            dist.broadcast(flag, src=0)
+            need = bool(flag.item() > 0.0)
+        if not need:
+            break
+        optimizer.step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
     big = rows_out[-1]
     total_flops = sum(NS_BATCH * flops_newton_schulz(m, n) for m, n in NS_SHAPES)
@@ -549,13 +689,16 @@ def run_gpu_arm(args) -> None:
 
         optimizer.ema._flush_gpu = timed_flush
 
+    # nvidia-smi needs about a second to deliver its first sample: it is started before the warm-up
+    # steps (the same workload) and, after the timed region, the same steps go on untimed until ten
+    # samples exist, so short timed regions (27 ms steps on 8 GPUs) still get their clock record.
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         optimizer.step()
     barrier()
 
     # ---- timed region: exactly K steps, device time, max over ranks
-    sampler = ClockSampler(local)
-    sampler.start()
     launches_before = _native.launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -697,7 +840,7 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    parser.add_argument("--impl", choices=("b200", "reference", "reference-gpu"), default="b200")
     parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
@@ -708,12 +851,16 @@ def main() -> None:
     if args.config in ("gram-ns", "gemm-sustained"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": f"the {args.config} microbenchmark has no CPU arm"}))
+        elif args.impl == "reference-gpu" and args.config == "gram-ns":
+            run_reference_gpu_ns(args)
         elif args.config == "gram-ns":
             run_ns_microbench(args)
         else:
             run_gemm_sustained(args)
     elif args.impl == "reference":
         run_reference_arm(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu_arm(args)
     else:
         run_gpu_arm(args)
 
