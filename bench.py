@@ -516,17 +516,6 @@ def run_ns_microbench(args) -> None:
         del x, packed, scratch, work, y
         torch.cuda.empty_cache()
     launches = _native.launch_count() - launches_before
-    extra_deadline = time.time() + 4.0
-    while True:
-        need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
-        if distributed:   # every rank takes the same number of extra steps: rank 0 decides
-            flag = torch.tensor([1.0 if need else 0.0], device=device)
-            dist.broadcast(flag, src=0)
-            need = bool(flag.item() > 0.0)
-        if not need:
-            break
-        optimizer.step()
-        torch.cuda.synchronize()
     clocks = sampler.stop()
     big = rows_out[-1]
     total_flops = sum(NS_BATCH * flops_newton_schulz(m, n) for m, n in NS_SHAPES)
@@ -709,6 +698,17 @@ def run_gpu_arm(args) -> None:
     barrier()
     total_ms = start.elapsed_time(end)
     launches = _native.launch_count() - launches_before
+    extra_deadline = time.time() + 4.0
+    while True:
+        need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
+        if distributed:   # every rank takes the same number of extra steps: rank 0 decides
+            flag = torch.tensor([1.0 if need else 0.0], device=device)
+            dist.broadcast(flag, src=0)
+            need = bool(flag.item() > 0.0)
+        if not need:
+            break
+        optimizer.step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
     if distributed:
         t = torch.tensor([total_ms], device=device)

@@ -65,7 +65,6 @@ size_t bytes_of(const Layout& l) {
   return l.wide_gram ? l.x_bytes + 5 * l.g_bytes : 2 * l.x_bytes + 2 * l.g_bytes;
 }
 
-float half_round(double v) { return __half2float(__float2half_rn(float(v))); }
 
 }  // namespace
 }  // namespace dionw
@@ -136,9 +135,11 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
                                      nullptr, 0.0f, dt, stream));
       }
       const bool fresh_q = (i == 0 || i == kRestart);
-      // Z = c G G^T + b G; on a fresh start also Q = Z + a I
+      // Z = c G G^T + b G; on a fresh start also Q = Z + a I.  The diagonal is round(fp32(Z) + fp32(a)),
+      // as the reference's compiled GPU step forms `z + a * eye` (its eager CPU run rounds `a` to
+      // fp16 first, which costs 4e-3 of accuracy on 256 x 4096 operands).
       DIONW_STEP(symmetric_product(g, nullptr, blocks, m, m, ldg, gb, 0, 0, g, ldg, gb, float(k.c), float(k.b), z, ldg, gb,
-                                   fresh_q ? q : nullptr, half_round(k.a), dt, stream));
+                                   fresh_q ? q : nullptr, float(k.a), dt, stream));
       if (!fresh_q) {
         // Q <- a Q + Q Z   (Z is stored symmetric, so Z^T == Z bit for bit)
         if (mirror)

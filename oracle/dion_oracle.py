@@ -148,8 +148,14 @@ def _sym2(a: Tensor, alpha: float, beta: float) -> Tensor:
     return torch.baddbmm(a, a, a.mT, beta=beta, alpha=alpha)
 
 
-def _gram_wide(x: Tensor) -> Tensor:
-    """Gram iteration on wide fp16 ``[N, m, n]`` (src/dionw/_gram.py:50-69)."""
+def _gram_wide(x: Tensor, eager_diagonal: bool = False) -> Tensor:
+    """Gram iteration on wide fp16 ``[N, m, n]`` (src/dionw/_gram.py:50-69).
+
+    ``Q = Z + a I`` (src/dionw/_gram.py:60-61): the reference's GPU step is compiled, and the fused
+    expression adds the fp32 coefficient to fp32(Z) and rounds once (the default here).  Its eager
+    run on the CPU evaluates ``a * eye`` in fp16 first, i.e. adds fp16(a): ``eager_diagonal=True``
+    reproduces that bit for bit (the CPU-written fixtures pin it).
+    """
     g = _sym1(x)
     eye = torch.eye(x.size(-2), dtype=x.dtype).expand_as(g)
     q = eye
@@ -160,7 +166,10 @@ def _gram_wide(x: Tensor) -> Tensor:
             g = _sym1(x)
         z = _sym2(g, alpha=c, beta=b)
         if i in (0, RESTART_AT):
-            q = z + a * eye
+            if eager_diagonal:
+                q = z + a * eye
+            else:
+                q = (z.float() + torch.tensor(a, dtype=torch.float32) * eye.float()).to(z.dtype)
         else:
             q = torch.baddbmm(q, q, z, beta=a)
         if i < last and i + 1 != RESTART_AT:
@@ -178,17 +187,18 @@ def _gram_square(x: Tensor) -> Tensor:
     return x
 
 
-def gram_newton_schulz(matrix: Tensor, eps: float = NS_EPS) -> Tensor:
+def gram_newton_schulz(matrix: Tensor, eps: float = NS_EPS, eager_diagonal: bool = False) -> Tensor:
     """Polar factor of each matrix of ``[N, rows, cols]``; bf16 result.
 
     src/dionw/_gram.py:72-89: transpose tall inputs, normalise by the Frobenius
     norm (+eps) in fp32, iterate in fp16, return bf16 in the input orientation.
+    ``eager_diagonal``: see ``_gram_wide``.
     """
     tall = matrix.size(-2) > matrix.size(-1)
     x = (matrix.mT if tall else matrix).float()
     x = (x / (torch.linalg.vector_norm(x, dim=(-2, -1), keepdim=True) + eps)).half()
     x = x.contiguous()
-    x = _gram_wide(x) if x.size(-1) > x.size(-2) else _gram_square(x)
+    x = _gram_wide(x, eager_diagonal) if x.size(-1) > x.size(-2) else _gram_square(x)
     return (x.mT if tall else x).bfloat16()
 
 

@@ -1,0 +1,151 @@
+"""This package's step against the UNMODIFIED reference package running on the same GPU.
+
+The reference (JTriggerFish/dionw, its torch.compile + Triton + cuBLAS step) is not part of this
+repository.  When a copy of its package sits under ``baseline/_ref`` (git-ignored), these tests
+run both optimizers on identical seeded parameters and gradients and compare every step: the sets
+of selected rows exactly, weights and variance within rel-L2 2e-3 (the fp16 Newton-Schulz is
+involved), momentum, AdamW state and EMA shadows within 1e-5.  Without the copy, or if the
+reference does not run under the installed torch, they skip.
+"""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+from torch import nn
+
+from conftest import ROOT, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+REF_ROOT = Path(ROOT) / "baseline" / "_ref"
+
+
+@pytest.fixture(scope="module")
+def reference():
+    if not (REF_ROOT / "dionw" / "__init__.py").exists():
+        pytest.skip("no reference package under baseline/_ref")
+    sys.path.insert(0, str(REF_ROOT))
+    try:
+        import dionw as ref
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"the reference does not import here: {exc!r}")
+    finally:
+        sys.path.remove(str(REF_ROOT))
+    return ref
+
+
+class Net(nn.Module):
+    """Config 1's weight and bias, a second matrix shape that selects rows, one that does not,
+    and an embedding (AdamW with decay)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        gen = torch.Generator().manual_seed(0)
+        mk = lambda *shape: nn.Parameter(torch.randn(*shape, generator=gen) * 0.02)  # noqa: E731
+        self.weight = mk(1024, 4096)
+        self.bias = mk(4096)
+        self.tall = mk(4096, 1024)
+        self.small = mk(768, 2304)
+        self.table = nn.Embedding(512, 256)
+        with torch.no_grad():
+            self.table.weight.copy_(torch.randn(512, 256, generator=gen) * 0.02)
+
+
+def _selected_rows(momentum_before: torch.Tensor, grad: torch.Tensor, momentum_after: torch.Tensor) -> set[int]:
+    """Rows whose momentum was decayed after the accumulation: the rows the step selected."""
+    accumulated = momentum_before + grad
+    changed = (momentum_after != accumulated).any(dim=1)
+    return set(torch.nonzero(changed).flatten().tolist())
+
+
+@pytest.mark.parametrize("with_ema", [False, True])
+def test_steps_match_the_reference_running_on_this_gpu(reference, with_ema) -> None:
+    import dionw_b200 as ours
+
+    def build(pkg):
+        net = Net().to(DEV)
+        groups, _ = pkg.param_groups(net)
+        ema = pkg.EMAConfig(decay=0.99, device=pkg.EMADevice.GPU) if with_ema else None
+        return net, pkg.Dion(groups, lr=3e-4, weight_decay=0.05, ema=ema)
+
+    try:
+        ref_net, ref_opt = build(reference)
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"the reference does not build here: {exc!r}")
+    our_net, our_opt = build(ours)
+    matrices = ("weight", "tall", "small")
+    gen = torch.Generator().manual_seed(1)
+    for step in range(4):
+        before = {n: ref_opt.state[getattr(ref_net, n)].get("momentum") for n in matrices}
+        before = {n: (torch.zeros_like(getattr(ref_net, n)) if v is None else v.detach().clone())
+                  for n, v in before.items()}
+        ours_before = {n: our_opt.state[getattr(our_net, n)].get("momentum") for n in matrices}
+        ours_before = {n: (torch.zeros_like(getattr(our_net, n)) if v is None else v.detach().clone())
+                       for n, v in ours_before.items()}
+        grads = {}
+        for (name, p_ref), (_, p_our) in zip(ref_net.named_parameters(), our_net.named_parameters()):
+            g = (torch.randn(p_ref.shape, generator=gen) * 1e-3).to(DEV)
+            p_ref.grad, p_our.grad = g.clone(), g.clone()
+            grads[name] = g
+        try:
+            ref_opt.step()
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"the reference's step does not run under torch {torch.__version__}: {exc!r}")
+        our_opt.step()
+        torch.cuda.synchronize()
+        for name in matrices:
+            p_ref, p_our = getattr(ref_net, name), getattr(our_net, name)
+            s_ref, s_our = ref_opt.state[p_ref], our_opt.state[p_our]
+            if name != "small":   # 768 rows < 1024: every row is updated, nothing is selected
+                rows_ref = _selected_rows(before[name], grads[name], s_ref["momentum"])
+                rows_our = _selected_rows(ours_before[name], grads[name], s_our["momentum"])
+                assert rows_ref == rows_our, (step, name, len(rows_ref ^ rows_our))
+                assert len(rows_our) == p_our.shape[0] // 4
+            assert rel_l2(s_our["momentum"], s_ref["momentum"]) <= 1e-5, (step, name)
+            assert rel_l2(s_our["variance"], s_ref["variance"]) <= 2e-3, (step, name)
+            assert rel_l2(p_our, p_ref) <= 2e-3, (step, name)
+        for name in ("bias", "table.weight"):
+            p_ref, p_our = dict(ref_net.named_parameters())[name], dict(our_net.named_parameters())[name]
+            assert rel_l2(p_our, p_ref) <= 1e-5, (step, name)
+            for key in ("exp_avg", "exp_avg_sq"):
+                assert rel_l2(our_opt.state[p_our][key], ref_opt.state[p_ref][key]) <= 1e-5, (step, name, key)
+        if with_ema:
+            for (name, p_ref), (_, p_our) in zip(ref_net.named_parameters(), our_net.named_parameters()):
+                a, b = our_opt.state[p_our]["ema_shadow"], ref_opt.state[p_ref]["ema_shadow"]
+                tolerance = 1e-5 if name in ("bias", "table.weight") else 2e-3
+                assert rel_l2(a, b) <= tolerance, (step, name)
+    # the update itself, not just W (which the unchanged rows dominate)
+    fresh = Net()
+    for name in matrices:
+        start = getattr(fresh, name).detach().to(DEV)
+        delta_ref, delta_our = getattr(ref_net, name).detach() - start, getattr(our_net, name).detach() - start
+        assert rel_l2(delta_our, delta_ref) <= 1e-2, name
+
+
+def test_gram_newton_schulz_matches_the_reference_entry(reference) -> None:
+    """The public orthogonalization entry on the same batch: bf16 results within the rounding of two
+    fp16 evaluations, and the same orthogonality error."""
+    from dionw_b200.newton_schulz import gram_polar_express
+
+    fn = reference.newton_schulz.newton_schulz_fn(reference.NewtonSchulz.GRAM)
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    for shape in ((4, 1024, 4096), (2, 512, 512), (3, 2304, 768)):
+        x = torch.randn(*shape, device=DEV, generator=gen)
+        try:
+            theirs = fn(x, 1e-8)
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"the reference's Newton-Schulz does not run here: {exc!r}")
+        mine = gram_polar_express(x, 1e-8)
+        assert mine.dtype == theirs.dtype == torch.bfloat16 and mine.shape == theirs.shape
+        assert rel_l2(mine, theirs) <= 5e-3, shape
+        wide = (lambda y: y if y.shape[-2] <= y.shape[-1] else y.mT)
+        eye = torch.eye(min(shape[1:]), device=DEV)
+        err_mine = float(torch.linalg.matrix_norm(wide(mine.float()) @ wide(mine.float()).mT - eye).max())
+        err_theirs = float(torch.linalg.matrix_norm(wide(theirs.float()) @ wide(theirs.float()).mT - eye).max())
+        assert abs(err_mine - err_theirs) <= 0.02 * err_theirs + 0.02, (shape, err_mine, err_theirs)
