@@ -149,3 +149,71 @@ def test_gram_newton_schulz_matches_the_reference_entry(reference) -> None:
         err_mine = float(torch.linalg.matrix_norm(wide(mine.float()) @ wide(mine.float()).mT - eye).max())
         err_theirs = float(torch.linalg.matrix_norm(wide(theirs.float()) @ wide(theirs.float()).mT - eye).max())
         assert abs(err_mine - err_theirs) <= 0.02 * err_theirs + 0.02, (shape, err_mine, err_theirs)
+
+
+@pytest.mark.parametrize("kind", ["polar_express", "polar_express_triton", "keller", "keller_triton"])
+def test_bf16_kinds_round_like_the_reference_on_this_gpu(reference, kind) -> None:
+    """The bf16 iterations (src/dionw/_polar_express.py:38-104): distance to the same polynomials in
+    fp64, here and in the reference, on a wide, a tall and a square batch."""
+    import dionw_b200 as ours
+    from oracle import dion_oracle as oracle
+
+    theirs_fn = reference.newton_schulz.newton_schulz_fn(reference.NewtonSchulz(kind))
+    ours_fn = ours.newton_schulz.newton_schulz_fn(ours.NewtonSchulz(kind))
+    coeffs, safety = ((oracle.POLAR_EXPRESS_COEFFS, 1.02) if kind.startswith("polar") else (oracle.KELLER_COEFFS, 1.0))
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    for shape in ((3, 256, 1024), (2, 1536, 512), (2, 640, 640)):
+        x = torch.randn(*shape, device=DEV, generator=gen)
+        try:
+            theirs = theirs_fn(x, 1e-7)
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"the reference's {kind} does not run here: {exc!r}")
+        mine = ours_fn(x, 1e-7)
+        wide = x if shape[1] <= shape[2] else x.mT
+        t = wide.double()
+        t = t / (t.norm(dim=(-2, -1), keepdim=True) * safety + 1e-7)
+        for a, b, c in coeffs:
+            g = t @ t.mT
+            t = a * t + (b * g + c * g @ g) @ t
+        target = t if shape[1] <= shape[2] else t.mT
+        err_mine, err_theirs = rel_l2(mine, target), rel_l2(theirs, target)
+        assert mine.dtype == torch.bfloat16 and mine.shape == theirs.shape
+        assert err_mine <= 1.3 * err_theirs + 3e-3, (kind, shape, err_mine, err_theirs)
+
+
+def test_muon_update_matches_the_reference_on_this_gpu(reference) -> None:
+    """MUON_UPDATE (Keller iteration in bf16, Nesterov momentum, no row normalization, every row)."""
+    import dionw_b200 as ours
+
+    def build(pkg):
+        net = Net().to(DEV)
+        groups, _ = pkg.param_groups(net, fraction=1.0)
+        return net, pkg.Dion(groups, lr=3e-4, weight_decay=0.05, matrix_update=pkg.MUON_UPDATE)
+
+    try:
+        ref_net, ref_opt = build(reference)
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"the reference does not build here: {exc!r}")
+    our_net, our_opt = build(ours)
+    gen = torch.Generator().manual_seed(2)
+    start = {n: p.detach().clone() for n, p in our_net.named_parameters()}
+    for step in range(3):
+        for (_, p_ref), (_, p_our) in zip(ref_net.named_parameters(), our_net.named_parameters()):
+            g = (torch.randn(p_ref.shape, generator=gen) * 1e-3).to(DEV)
+            p_ref.grad, p_our.grad = g.clone(), g.clone()
+        try:
+            ref_opt.step()
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"the reference's Muon step does not run under torch {torch.__version__}: {exc!r}")
+        our_opt.step()
+        torch.cuda.synchronize()
+        for (name, p_ref), (_, p_our) in zip(ref_net.named_parameters(), our_net.named_parameters()):
+            matrix = name in ("weight", "tall", "small")
+            assert rel_l2(p_our, p_ref) <= (2e-3 if matrix else 1e-5), (step, name)
+            if matrix:
+                assert rel_l2(our_opt.state[p_our]["momentum"], ref_opt.state[p_ref]["momentum"]) <= 1e-5, (step, name)
+    for name in ("weight", "tall", "small"):
+        p_ref, p_our = getattr(ref_net, name), getattr(our_net, name)
+        # bf16 iterations: the two updates differ by bf16 rounding of five steps
+        assert rel_l2(p_our.detach() - start[name], p_ref.detach() - start[name]) <= 3e-2, name
