@@ -34,7 +34,7 @@ def load_golden(name: str) -> dict[str, torch.Tensor]:
 
 def rel_l2(value: torch.Tensor, target: torch.Tensor) -> float:
     """``|value - target| / |target|`` in the Frobenius norm (0/0 counts as 0)."""
-    value, target = value.double().cpu(), target.double().cpu()
+    value, target = value.detach().double().cpu(), target.detach().double().cpu()
     denom = float(target.norm())
     diff = float((value - target).norm())
     return diff if denom == 0.0 else diff / denom
