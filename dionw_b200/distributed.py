@@ -51,7 +51,7 @@ from dionw_b200.routing import RouteKind
 
 SHARD_KEY = "_dionw_shard"   # top-level entry of a per-rank checkpoint
 
-__all__ = ["SHARD_KEY", "ShardedDion", "assign_by_cost", "newton_schulz_cost", "shard_range", "split_runs"]
+__all__ = ["SHARD_KEY", "ShardedDion", "assign_by_cost", "is_cut", "newton_schulz_cost", "shard_range", "split_runs"]
 
 # AdamW tensors at least this large are cut into per-rank element ranges.
 ADAMW_SHARD_MIN_ELEMENTS = 1 << 20
@@ -101,6 +101,13 @@ def split_runs(sizes: Sequence[int | None], limit: int) -> list[list[int]]:
     if current:
         runs.append(current)
     return runs
+
+
+def is_cut(numel: int, world: int, contiguous: bool, multiple: int = 1) -> bool:
+    """Whether a tensor of ``numel`` elements is kept as one element range per rank: more than one
+    rank, at least ``ADAMW_SHARD_MIN_ELEMENTS`` elements, contiguous, and a size that divides into
+    ``world`` ranges of a multiple of ``multiple`` elements (4 keeps fp32 ranges 16-byte aligned)."""
+    return world > 1 and numel >= ADAMW_SHARD_MIN_ELEMENTS and numel % (multiple * world) == 0 and contiguous
 
 
 def shard_range(numel: int, rank: int, world: int) -> tuple[int, int]:
@@ -158,8 +165,7 @@ class _ShardedCore(_DionCore):
     # ---- layout --------------------------------------------------------------
     def _is_cut(self, param: Tensor) -> bool:
         """Whether an AdamW tensor is updated by element range rather than whole on every rank."""
-        n = param.numel()
-        return self._world > 1 and n >= ADAMW_SHARD_MIN_ELEMENTS and n % self._world == 0 and param.is_contiguous()
+        return is_cut(param.numel(), self._world, param.is_contiguous())
 
     def _new_adamw_state(self, param: Tensor) -> None:
         entry = self.state[param]
@@ -411,9 +417,7 @@ class _ShardedCore(_DionCore):
     # ---- EMA shards ------------------------------------------------------------
     def _ema_is_cut(self, param: Tensor) -> bool:
         """Whether the EMA keeps only this rank's element range of ``param``'s shadow."""
-        n = param.numel()   # ranges of a multiple of four floats keep every range 16-byte aligned
-        return (self._world > 1 and n >= ADAMW_SHARD_MIN_ELEMENTS and n % (4 * self._world) == 0
-                and param.is_contiguous())
+        return is_cut(param.numel(), self._world, param.is_contiguous(), multiple=4)
 
     def _ema_view(self, param: Tensor) -> Tensor:
         if not self._ema_is_cut(param):

@@ -87,3 +87,69 @@ def test_two_ranks_exchange_run_results_over_gloo() -> None:
         p.join(120)
         assert p.exitcode == 0
     assert failures.empty(), failures.get()
+
+
+def test_cut_predicate() -> None:
+    from dionw_b200.distributed import ADAMW_SHARD_MIN_ELEMENTS, is_cut
+
+    big = ADAMW_SHARD_MIN_ELEMENTS
+    assert not is_cut(big, 1, True)                      # one rank: nothing is cut
+    assert is_cut(big, 8, True) and is_cut(big, 8, True, multiple=4)
+    assert not is_cut(big - 8, 8, True)                  # too small
+    assert not is_cut(big + 4, 8, True)                  # does not divide into 8 ranges
+    assert is_cut(big + 8, 8, True) and not is_cut(big + 8, 8, True, multiple=4)   # ranges not 16-byte aligned
+    assert not is_cut(big, 8, False)                     # not contiguous
+    assert [shard_range(64, r, 4) for r in range(4)] == [(0, 16), (16, 32), (32, 48), (48, 64)]
+
+
+def _ema_shard_worker(rank: int, world: int, port: int, failures) -> None:
+    """The EMA range helpers of ``ShardedDion`` on CPU tensors over gloo (no kernel involved)."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from dionw_b200 import distributed
+        from dionw_b200.distributed import ShardedDion
+
+        distributed.ADAMW_SHARD_MIN_ELEMENTS = 64
+        opt = ShardedDion.__new__(ShardedDion)
+        opt._dist, opt._pg, opt._world, opt._rank = dist, None, world, rank
+        gen = torch.Generator().manual_seed(0)
+        big = torch.randn(16, 8, generator=gen)           # 128 elements: cut into two ranges of 64
+        small = torch.randn(5, 3, generator=gen)          # whole on every rank
+        assert opt._ema_is_cut(big) and not opt._ema_is_cut(small)
+        view = opt._ema_view(big)
+        assert view.shape == (64,) and view.data_ptr() == big.view(-1)[64 * rank:].data_ptr()
+        assert opt._ema_view(small) is small
+        # a rank's shadow range, gathered into the reference layout
+        shard = view.clone() * 2.0
+        whole = opt._gather_shadow(big, shard)
+        assert whole.shape == big.shape and torch.equal(whole, big * 2.0)
+        # a loaded full shadow is cut back to this rank's range; a range stays a range
+        assert torch.equal(opt._loaded_shadow_share(big, whole), shard)
+        assert opt._loaded_shadow_share(big, shard) is shard
+        assert opt._loaded_shadow_share(small, small) is small
+        # swap: every replica receives all ranges; restore brings the live values back
+        live = big.clone()
+        kept = opt._swap_in(big, shard)
+        assert torch.equal(big, live * 2.0) and torch.equal(kept, live.view(-1)[64 * rank: 64 * rank + 64])
+        opt._swap_out(big, kept)
+        assert torch.equal(big, live)
+    except Exception as exc:  # reported to the parent
+        import traceback
+        failures.put(f"rank {rank}: {exc!r}\n{traceback.format_exc()}")
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_ema_ranges_gather_and_swap_over_gloo() -> None:
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_ema_shard_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert failures.empty(), failures.get()
+    assert all(p.exitcode == 0 for p in procs)
