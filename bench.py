@@ -516,6 +516,8 @@ def run_ns_microbench(args) -> None:
         del x, packed, scratch, work, y
         torch.cuda.empty_cache()
     launches = _native.launch_count() - launches_before
+    if replay:   # a replayed step executes the kernels of its recording without passing the library's counter
+        launches += (optimizer.graph_replays - replays_before) * optimizer.graph_kernels
     clocks = sampler.stop()
     big = rows_out[-1]
     total_flops = sum(NS_BATCH * flops_newton_schulz(m, n) for m, n in NS_SHAPES)
@@ -660,7 +662,11 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize()
 
     timer = StageTimer()
-    _matrix_step.STAGE_HOOK = timer
+    replay = bool(args.graph_replay) and not distributed
+    if replay:
+        optimizer.graph_replay = True   # the stage hook is installed only while stages are timed
+    else:
+        _matrix_step.STAGE_HOOK = timer
     real_adamw = _adamw.adamw_step
 
     def timed_adamw(group, state):
@@ -689,6 +695,7 @@ def run_gpu_arm(args) -> None:
 
     # ---- timed region: exactly K steps, device time, max over ranks
     launches_before = _native.launch_count()
+    replays_before = optimizer.graph_replays if replay else 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record()
@@ -698,6 +705,8 @@ def run_gpu_arm(args) -> None:
     barrier()
     total_ms = start.elapsed_time(end)
     launches = _native.launch_count() - launches_before
+    if replay:   # a replayed step executes the kernels of its recording without passing the library's counter
+        launches += (optimizer.graph_replays - replays_before) * optimizer.graph_kernels
     extra_deadline = time.time() + 4.0
     while True:
         need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
@@ -718,12 +727,15 @@ def run_gpu_arm(args) -> None:
 
     # ---- per-stage device time (separate steps so the events do not sit in the timed region)
     timer.enabled = True
+    _matrix_step.STAGE_HOOK = timer
     stage_steps = max(1, min(3, args.steps))
     for _ in range(stage_steps):
         with timer("whole_step"):
             optimizer.step()
     stages = {k: v / stage_steps for k, v in timer.collect().items()}
     timer.enabled = False
+    if replay:
+        _matrix_step.STAGE_HOOK = None
     whole_ms = stages.pop("whole_step", None)   # the same steps, bracketed once: shows what lies between the stages
 
     # ---- host dispatch: wall time for step() to return with the GPU idle at the start and
@@ -806,6 +818,8 @@ def run_gpu_arm(args) -> None:
                    "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
                                      "round_elements": int(optimizer.round_elements)} if distributed else None),
                    "ema": "GPU shadows, decay 0.9999, every step" if ema is not None else None,
+                   "graph_replay": ({"recordings": optimizer._graph_recordings, "kernels_per_replay": optimizer.graph_kernels}
+                                    if replay else None),
                    "gradients": ("one tensor per shape shared by all layers (weights + gradients would not fit "
                                  "beside the state)" if shared_grads else "one tensor per parameter")},
         "roofline": {
@@ -844,6 +858,9 @@ def main() -> None:
     parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--graph-replay", action="store_true",
+                        help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
+                             "counts only the steps that ran as launches")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     parser.add_argument("--overlap-apply", action="store_true",
                         help="sharded step: weight update of a round on a side stream beside the next round")

@@ -17,6 +17,9 @@ from torch import Tensor
 
 _ALIGN = 256
 _arenas: dict[tuple[torch.device, str], Tensor] = {}
+# Bumped whenever an arena is allocated, regrown or dropped: a recorded CUDA graph holds arena
+# addresses and is only valid while this number stands.
+generation = 0
 
 Plan = dict[str, tuple[tuple[int, ...], torch.dtype]]
 
@@ -51,6 +54,8 @@ def arena(device: torch.device, nbytes: int, name: str = "run") -> Tensor:
     key = (device, name)
     buffer = _arenas.get(key)
     if buffer is None or buffer.numel() < nbytes:
+        global generation
+        generation += 1
         _arenas.pop(key, None)
         buffer = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _arenas[key] = buffer
@@ -65,4 +70,6 @@ def carve(device: torch.device, plan: Plan, name: str = "run") -> dict[str, Tens
 
 def release() -> None:
     """Drop every arena (tests, or before a memory-hungry phase)."""
+    global generation
+    generation += 1
     _arenas.clear()

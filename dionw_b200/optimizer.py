@@ -144,6 +144,11 @@ class _DionCore(Optimizer):
         }
         self._buckets: list[Bucket] | None = None
         self._side_streams: dict[torch.device, torch.cuda.Stream] = {}
+        self._graph: tuple[tuple[Any, ...], torch.cuda.CUDAGraph] | None = None
+        self._graph_warm: tuple[Any, ...] | None = None
+        self._graph_recordings = 0
+        self.graph_kernels = 0   # kernel launches held by the current recording
+        self.graph_replays = 0   # steps executed by replaying a recording
         super().__init__(params, defaults)
 
     def add_param_group(self, param_group: dict[str, Any]) -> None:
@@ -216,13 +221,95 @@ class _DionCore(Optimizer):
                 loss = closure()
         runs = [(bucket, run) for bucket in self._ensure_buckets() for run in self._runs_of(bucket)]
         devices = {bucket.momentum.device for bucket, _ in runs}
-        if self.overlap_streams and len(runs) > 1 and len(devices) == 1 and step_run is _sequential_step_run:
+        if self.graph_replay and self._graph_eligible(runs):
+            self._step_replayed(runs)
+        elif self.overlap_streams and len(runs) > 1 and len(devices) == 1 and step_run is _sequential_step_run:
             self._step_overlapped(runs, devices.pop())
         else:
-            for bucket, run in runs:
-                step_run(bucket, run, self.param_groups[bucket.group_index], self.state)
-            self._step_adamw_groups()
+            self._step_in_sequence(runs)
         return loss
+
+    def _step_in_sequence(self, runs: list[tuple[Bucket, list[int]]]) -> None:
+        for bucket, run in runs:
+            step_run(bucket, run, self.param_groups[bucket.group_index], self.state)
+        self._step_adamw_groups()
+
+    # Optional replay of the step from a CUDA graph.  The reference measures 7-17 ms of host
+    # dispatch per step of its own (README.md:514-516, bench/host_dispatch.py:28-56); here a step
+    # is a few hundred launches through ctypes.  With ``graph_replay = True`` the first step of a
+    # configuration runs as launches (it creates state, grows the scratch arenas and does the
+    # one-time device set-up), the second is recorded on a capture stream and replayed, and every
+    # later one is a single ``cudaGraphLaunch``.  A recording holds addresses and host scalars by
+    # value, so it is keyed on everything a step reads from the host: which parameters have
+    # gradients and where parameters, gradients, state and arenas lie, and each group's lr,
+    # weight decay, momentum, betas and eps.  Any change (a learning-rate schedule, gradients
+    # reallocated by ``zero_grad(set_to_none=True)``) costs one step as launches and one new
+    # recording; after ``GRAPH_RECORDINGS_MAX`` recordings the optimizer stops recording and
+    # steps as launches, since a loop that changes every step gains nothing from a graph.
+    # Keep gradients in place (``zero_grad(set_to_none=False)``) and change lr rarely to use it.
+    # The arithmetic is the same kernels in the same order: results are bit-identical.
+    graph_replay = False
+    GRAPH_RECORDINGS_MAX = 8
+
+    def _graph_eligible(self, runs: list[tuple[Bucket, list[int]]]) -> bool:
+        """Whether this step can be recorded: one CUDA device, the built-in stages, nothing that
+        makes the step allocate (packed copies of strided tensors, dtype casts of gradients)."""
+        from dionw_b200 import _matrix_step
+        from dionw_b200.newton_schulz import NativeOrthogonalizer
+
+        if self.overlap_streams:
+            return False
+        if step_run is not _sequential_step_run or _matrix_step.STAGE_HOOK is not None:
+            return False
+        devices = set()
+        for group in self.param_groups:
+            for param in group["params"]:
+                grad = param.grad
+                if grad is None:
+                    continue
+                if not (param.is_contiguous() and grad.is_contiguous() and grad.dtype is torch.float32):
+                    return False
+                devices.add(param.device)
+        return len(devices) == 1 and all(isinstance(b.orthogonalize, NativeOrthogonalizer) for b, _ in runs)
+
+    def _step_signature(self, runs: list[tuple[Bucket, list[int]]]) -> tuple[Any, ...]:
+        """Everything a recorded step bakes in (see ``graph_replay``)."""
+        from dionw_b200 import _workspace
+
+        parts: list[Any] = [_workspace.generation, torch.cuda.current_device()]
+        for group in self.param_groups:
+            parts.append((float(group["lr"]), float(group["weight_decay"]), float(group[MOMENTUM_KEY]),
+                          float(group[MUON_BETA2_KEY]), tuple(map(float, group["betas"])), float(group["eps"])))
+            parts.append(tuple((p.data_ptr(), p.grad.data_ptr()) for p in group["params"] if p.grad is not None))
+        for bucket, run in runs:
+            parts.append((bucket.momentum.data_ptr(), bucket.variance.data_ptr(), tuple(run)))
+        return tuple(parts)
+
+    def _step_replayed(self, runs: list[tuple[Bucket, list[int]]]) -> None:
+        signature = self._step_signature(runs)
+        if self._graph is not None and self._graph[0] == signature:
+            self._graph[1].replay()
+            self.graph_replays += 1
+            return
+        self._graph = None
+        if self._graph_recordings >= self.GRAPH_RECORDINGS_MAX:
+            self._step_in_sequence(runs)
+            return
+        if self._graph_warm != signature:
+            self._step_in_sequence(runs)
+            self._graph_warm = self._step_signature(runs)  # the arenas may have grown
+            return
+        from dionw_b200 import _native
+
+        graph = torch.cuda.CUDAGraph()
+        before = _native.launch_count()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            self._step_in_sequence(runs)
+        self.graph_kernels = _native.launch_count() - before
+        graph.replay()
+        self.graph_replays += 1
+        self._graph = (signature, graph)
+        self._graph_recordings += 1
 
     def _step_adamw_groups(self) -> None:
         for group in self.param_groups:

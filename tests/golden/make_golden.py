@@ -200,7 +200,9 @@ def _routing_case(dionw) -> None:
 
 def main() -> None:
     torch.set_num_threads(1)  # one summation order for every run of this script
-    dionw, matrix_step, plain = _import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    dionw, matrix_step, plain = _import_reference(sys.argv[1])
     _step_case(dionw, matrix_step, "step_selected", [(64, 192), (64, 192), (128, 64)],
                fraction=0.25, min_dim=32)
     _step_case(dionw, matrix_step, "step_full_rows", [(96, 160), (160, 96), (64, 64)],

@@ -676,3 +676,32 @@ def test_mixin_on_a_stock_optimizer_with_bf16_parameters() -> None:
     shadow = opt.state[net.weight]["ema_shadow"]
     assert shadow.dtype == torch.float32 and shadow.is_cuda
     assert opt.swap_ema_weights() and opt.restore_non_ema_weights()
+
+
+def test_remaining_refusals_carry_the_reference_messages() -> None:
+    """The refusals no other test reaches: a non-float32 CUDA parameter (src/dionw/optimizer.py:201-209),
+    a run holding a parameter without a gradient (src/dionw/_matrix_step.py:129-130), and the two
+    partial EMA swaps (src/dionw/ema/_swap.py:43-101)."""
+    half = nn.Linear(32, 16).to(DEV).half()
+    with pytest.raises(TypeError, match="float32 parameters"):
+        dionw.Dion(dionw.param_groups(half).groups, lr=1e-3)
+
+    net = nn.Linear(32, 16).to(DEV)
+    opt = dionw.Dion(dionw.param_groups(net).groups, lr=1e-2, ema=EMAConfig(decay=0.5))
+    from dionw_b200 import _matrix_step
+
+    net.weight.grad = None
+    bucket = opt._ensure_buckets()[0]
+    with pytest.raises(RuntimeError, match="a Dion run holds a parameter without a gradient"):
+        _matrix_step.step_run(bucket, [0], opt.param_groups[bucket.group_index], opt.state)
+
+    for p in net.parameters():
+        p.grad = torch.randn_like(p)
+    opt.step()
+    frozen = nn.Linear(4, 4).to(DEV).requires_grad_(False)
+    with pytest.raises(ValueError, match="no optimizer-managed parameters"):
+        opt.swap_ema_weights(frozen)
+    del opt.state[net.bias]["ema_shadow"]
+    with pytest.raises(RuntimeError, match="Refusing to mix live and EMA weights"):
+        opt.swap_ema_weights()
+    assert not opt.ema_weights_swapped
