@@ -46,6 +46,9 @@ CONFIGS = {
     "llama3-70b-1layer": (1, 8192, 1024, 28672, 16032),
     # GPT-2-small (12 layers, d = 768, ~124 M parameters): the shapes are fixed in Gpt2Shaped
     "gpt2-small": (12, 768, 768, 3072, 50257),
+    # one fp32 weight 1024 x 4096 (Dion3, k = 256) and a bias[4096] (AdamW): small enough for the
+    # CPU arm to run the whole workload, unscaled; the shapes are fixed in SingleMatrix
+    "single-1024x4096": (1, 4096, 1024, 0, 0),
 }
 EMBED_ONLY_WITH_EMA = {"llama3-70b-20layers", "llama3-70b-1layer"}
 # Above this many bytes of fp32 weights + gradients per GPU the gradients are one tensor per
@@ -107,6 +110,26 @@ class Gpt2Shaped(nn.Module):
         self.lm_head = None
 
     init_ = LlamaShaped.init_
+
+
+class SingleMatrix(nn.Module):
+    """One weight 1024 x 4096 and one bias[4096]."""
+
+    def __init__(self, device) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(1024, 4096, device=device))
+        self.norm = nn.Parameter(torch.empty(4096, device=device))   # the bias: AdamW, no decay
+        self.lm_head = None
+
+    init_ = LlamaShaped.init_
+
+
+def build_model(config: str, device) -> nn.Module:
+    if config == "gpt2-small":
+        return Gpt2Shaped(device)
+    if config == "single-1024x4096":
+        return SingleMatrix(device)
+    return LlamaShaped(config, device)
 
 
 def flops_newton_schulz(m: int, n: int) -> float:
@@ -273,6 +296,9 @@ def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
         shapes = [(d, 3 * d), (d, d), (d, 4 * d), (4 * d, d)]       # one whole layer
         per_layer = shapes
         what = f"one layer's c_attn, c_proj, fc, proj blocks + one LayerNorm weight[{d}]"
+    elif config == "single-1024x4096":
+        shapes = per_layer = [(1024, 4096)]                          # the whole workload
+        what = "the whole workload: the 1024x4096 weight + bias[4096]"
     else:
         shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
         per_layer = [(d, d)] * 2 + [(dkv, d)] * 2 + [(dff, d)] * 2 + [(d, dff)]
@@ -317,7 +343,9 @@ def run_reference_arm(args) -> None:
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["value"],
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp32 state, fp16 Newton-Schulz", "data": "synthetic",
-        "config": {"workload": args.config, "arm": "reference's algorithm on host CPU cores (oracle port)"},
+        "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
+                   "lr": LR, "weight_decay": WEIGHT_DECAY,
+                   "arm": "reference's algorithm on host CPU cores (oracle port)"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -351,7 +379,7 @@ def run_reference_gpu_arm(args) -> None:
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
     try:
-        model = Gpt2Shaped(device) if args.config == "gpt2-small" else LlamaShaped(args.config, device)
+        model = build_model(args.config, device)
         model.init_(seed=0)
         routes = {} if model.lm_head is None else {model.lm_head.weight: reference.Route(reference.RouteKind.ADAMW)}
         groups, _ = reference.param_groups(model, routes=routes)
@@ -624,7 +652,7 @@ def run_gpu_arm(args) -> None:
     if need > have:
         raise SystemExit(f"bench.py: config {args.config} needs about {need / 1e9:.0f} GB per GPU on {world} GPU(s), "
                          f"this GPU has {have / 1e9:.0f} GB: run it on more GPUs")
-    model = Gpt2Shaped(device) if args.config == "gpt2-small" else LlamaShaped(args.config, device)
+    model = build_model(args.config, device)
     model.init_(seed=0)
     routes = {} if model.lm_head is None else {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
     groups, _ = dionw.param_groups(model, routes=routes)
