@@ -283,9 +283,13 @@ def measured_peaks() -> tuple[dict, str]:
 # the CPU arm (oracle) — also the cpu_baseline of the GPU arm
 # ---------------------------------------------------------------------------
 def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
-    """Times the CPU oracle on one layer's attention blocks (q, o: d x d; k, v: dkv x d) and
-    one RMSNorm vector, then scales the matrix time by Newton-Schulz FLOPs and the AdamW time
-    by elements to the whole parameter set."""
+    """Times the CPU oracle on a bounded sample of the workload and scales it to the whole set.
+
+    Matrix part: one whole layer's blocks, multiplied by the layer count, where a layer is
+    affordable (d_model <= 4096: about 3 s per sample step on 16 threads at the Llama-3-8B shapes);
+    for wider models the attention blocks alone, scaled by Newton-Schulz FLOPs.  AdamW part: a
+    slice of the embedding table (at most 2^24 elements) plus one norm vector, scaled by elements.
+    The single-matrix configuration is run whole."""
     from oracle import dion_oracle as oracle
 
     layers, d, dkv, dff, vocab = CONFIGS[config]
@@ -293,43 +297,59 @@ def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
     torch.set_num_threads(cores)
     gen = torch.Generator().manual_seed(0)
     if config == "gpt2-small":
-        shapes = [(d, 3 * d), (d, d), (d, 4 * d), (4 * d, d)]       # one whole layer
-        per_layer = shapes
-        what = f"one layer's c_attn, c_proj, fc, proj blocks + one LayerNorm weight[{d}]"
+        per_layer = [(d, 3 * d), (d, d), (d, 4 * d), (4 * d, d)]
+        shapes, what = per_layer, "one layer's c_attn, c_proj, fc, proj blocks"
+        adam_total = (vocab + 1024) * d + (4 * layers + 2) * d
     elif config == "single-1024x4096":
-        shapes = per_layer = [(1024, 4096)]                          # the whole workload
-        what = "the whole workload: the 1024x4096 weight + bias[4096]"
+        per_layer = shapes = [(1024, 4096)]
+        what = "the whole workload: the 1024x4096 weight"
+        adam_total = 4096
     else:
-        shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
         per_layer = [(d, d)] * 2 + [(dkv, d)] * 2 + [(dff, d)] * 2 + [(d, dff)]
-        what = f"one layer's q, o ({d}x{d}) and k, v ({dkv}x{d}) blocks + one RMSNorm[{d}]"
-    weights = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
-    norm = torch.randn(d, generator=gen) * 0.02
-    grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
-    gnorm = torch.randn(d, generator=gen) * 1e-3
-    opt = oracle.OracleDion(matrix=[(w, 0.25 if min(w.shape) >= 1024 else 1.0) for w in weights],
-                            adamw=[(norm, 0.0)], lr=LR, weight_decay=WEIGHT_DECAY)
-    times = []
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
-        opt.step(grads, [gnorm])
-        if i >= warmup:
-            times.append((time.perf_counter() - t0) * 1e3)
+        tables = 1 if config in EMBED_ONLY_WITH_EMA else 2
+        adam_total = tables * vocab * d + (2 * layers + 1) * d
+        if d <= 4096:
+            shapes, what = per_layer, f"one whole layer (q, o, k, v, gate, up, down at d = {d})"
+        else:
+            shapes = [(d, d), (d, d), (dkv, d), (dkv, d)]
+            what = f"one layer's q, o ({d}x{d}) and k, v ({dkv}x{d}) blocks"
 
     def block_flops(r: int, c: int) -> float:
         k = -(-r // 4) if min(r, c) >= 1024 else r
         return flops_newton_schulz(min(k, c), max(k, c))
 
+    def median_ms(step) -> float:
+        times = []
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            step()
+            if i >= warmup:
+                times.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(times)
+
+    weights = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
+    grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
+    matrices = oracle.OracleDion(matrix=[(w, 0.25 if min(w.shape) >= 1024 else 1.0) for w in weights],
+                                 adamw=[], lr=LR, weight_decay=WEIGHT_DECAY)
+    matrix_ms = median_ms(lambda: matrices.step(grads, []))
     sample_flops = sum(block_flops(r, c) for r, c in shapes)
     model_flops = layers * sum(block_flops(r, c) for r, c in per_layer)
-    per_step = statistics.median(times)
-    scaled = per_step * model_flops / sample_flops
+    matrix_scale = model_flops / sample_flops
+
+    adam_sample = min(adam_total, 1 << 24)
+    table = torch.randn(adam_sample, generator=gen) * 0.02
+    table_grad = torch.randn(adam_sample, generator=gen) * 1e-3
+    vectors = oracle.OracleDion(matrix=[], adamw=[(table, None)], lr=LR, weight_decay=WEIGHT_DECAY)
+    adam_ms = median_ms(lambda: vectors.step([], [table_grad]))
+    adam_scale = adam_total / adam_sample
+
+    scaled = matrix_ms * matrix_scale + adam_ms * adam_scale
     return {
         "value": scaled, "unit": "ms", "cores": cores, "kind": "port",
-        "sample": (f"CPU oracle (torch eager, {cores} threads) on {what}: "
-                   f"median {per_step:.1f} ms per sample step over {steps} steps, "
-                   f"scaled by Newton-Schulz FLOPs x{model_flops / sample_flops:.0f} to the whole set"),
-        "sample_ms": per_step,
+        "sample": (f"CPU oracle (torch eager, {cores} threads), median of {steps} steps after {warmup}: "
+                   f"{what}: {matrix_ms:.1f} ms x{matrix_scale:.0f} (Newton-Schulz FLOPs of the whole set / of the "
+                   f"sample); AdamW on {adam_sample} elements: {adam_ms:.2f} ms x{adam_scale:.1f} (elements)"),
+        "sample_ms": matrix_ms + adam_ms,
     }
 
 
@@ -656,7 +676,9 @@ def run_gpu_arm(args) -> None:
     model.init_(seed=0)
     routes = {} if model.lm_head is None else {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
     groups, _ = dionw.param_groups(model, routes=routes)
-    ema = dionw.EMAConfig(decay=0.9999, device=dionw.EMADevice.GPU) if args.config in EMBED_ONLY_WITH_EMA else None
+    ema_kind = args.ema if args.ema != "config" else ("gpu" if args.config in EMBED_ONLY_WITH_EMA else "none")
+    ema = None if ema_kind == "none" else dionw.EMAConfig(
+        decay=0.9999, device=dionw.EMADevice.GPU if ema_kind == "gpu" else dionw.EMADevice.CPU)
     if distributed:
         from dionw_b200.distributed import ShardedDion
 
@@ -703,6 +725,15 @@ def run_gpu_arm(args) -> None:
 
     import dionw_b200.optimizer as optimizer_module
     optimizer_module.adamw_step = timed_adamw
+    if ema_kind == "cpu":
+        # the snapshot kernel runs on the tracker's copy stream: the events land there
+        real_stage = _native.ema_stage_pack
+
+        def timed_stage(sources, offsets, staging):
+            with timer("ema_stage"):
+                real_stage(sources, offsets, staging)
+
+        _native.ema_stage_pack = timed_stage
     if optimizer.ema is not None:
         real_flush = optimizer.ema._flush_gpu
 
@@ -835,7 +866,13 @@ def run_gpu_arm(args) -> None:
     }
     if "ema" in stages:
         stage_report["ema"] = {"ms": stages["ema"], "GB/s": gbs("bytes_ema", "ema", share)}
-    cpu = cpu_sample_step(args.config, 5, 1) if world == 1 and not args.no_cpu_baseline else None
+    if "ema_stage" in stages:
+        # fp32 snapshot of every parameter written by one kernel into pinned host memory: bound by
+        # the host link (PCIe), not HBM; the worker thread's lerp on the host follows it
+        snapshot = 4.0 * (work["matrix_elements"] + work["adamw_elements"]) * share
+        stage_report["ema_stage"] = {"ms": stages["ema_stage"], "GB/s": snapshot / stages["ema_stage"] / 1e6,
+                                     "bound": "host link (device-to-host writes)", "bytes": snapshot}
+    cpu = cpu_sample_step(args.config, 3, 1) if world == 1 and not args.no_cpu_baseline else None
     line = {
         "metric": "optimizer_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
@@ -845,7 +882,10 @@ def run_gpu_arm(args) -> None:
                    "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)",
                    "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
                                      "round_elements": int(optimizer.round_elements)} if distributed else None),
-                   "ema": "GPU shadows, decay 0.9999, every step" if ema is not None else None,
+                   "ema": (None if ema is None else
+                           f"{ema_kind.upper()} shadows, decay 0.9999, every step"
+                           + (" (pinned host shadows, one snapshot kernel + host worker thread per step; the "
+                              "step waits for the previous update)" if ema_kind == "cpu" else "")),
                    "graph_replay": ({"recordings": optimizer._graph_recordings, "kernels_per_replay": optimizer.graph_kernels}
                                     if replay else None),
                    "gradients": ("one tensor per shape shared by all layers (weights + gradients would not fit "
@@ -886,6 +926,8 @@ def main() -> None:
     parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--ema", choices=("config", "none", "gpu", "cpu"), default="config",
+                        help="EMA of every parameter: 'config' = GPU shadows for the 70B-shaped configs, none otherwise")
     parser.add_argument("--graph-replay", action="store_true",
                         help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
                              "counts only the steps that ran as launches")
