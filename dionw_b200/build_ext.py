@@ -21,6 +21,8 @@ SOURCES = ("api.cu", "momentum.cu", "update.cu", "gemm.cu", "newton_schulz.cu", 
 FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-cudart", "static",
+    # host code: no fused multiply-adds the source does not spell out (the CPU EMA's lerp is bit-checked)
+    "-Xcompiler", "-ffp-contract=off",
 )
 
 

@@ -85,16 +85,56 @@ struct dionw_cpu_ema_job {
 
 namespace {
 
+// The two forms of the difference-form lerp (src/dionw/ema/_update.py:17-70 there; torch's
+// lerp picks them by |weight| < 0.5).  The small-weight form is one fused multiply-add per
+// element; without an FMA instruction in the compile target that is a libm call per element
+// (2.3 ns each, measured: 160 ms for 567 M elements on 8 threads), so on x86-64 the same loops
+// are also compiled for AVX2 + FMA and chosen at run time.  Both builds give the same bits:
+// the fused multiply-add is exactly rounded either way, and the large-weight form is compiled
+// with floating-point contraction off.
+inline void lerp_small_body(float* __restrict__ shadow, const float* __restrict__ staged, int64_t n, float weight) {
+  for (int64_t i = 0; i < n; ++i) shadow[i] = __builtin_fmaf(weight, staged[i] - shadow[i], shadow[i]);
+}
+
+inline void lerp_large_body(float* __restrict__ shadow, const float* __restrict__ staged, int64_t n, float keep) {
+  for (int64_t i = 0; i < n; ++i) shadow[i] = staged[i] - (staged[i] - shadow[i]) * keep;
+}
+
+#if defined(__x86_64__) && defined(__GNUC__)
+__attribute__((target("avx2,fma"))) void lerp_small_fma(float* __restrict__ shadow, const float* __restrict__ staged,
+                                                        int64_t n, float weight) {
+  for (int64_t i = 0; i < n; ++i) shadow[i] = __builtin_fmaf(weight, staged[i] - shadow[i], shadow[i]);
+}
+
+__attribute__((target("avx2,fma"))) void lerp_large_fma(float* __restrict__ shadow, const float* __restrict__ staged,
+                                                        int64_t n, float keep) {
+  for (int64_t i = 0; i < n; ++i) shadow[i] = staged[i] - (staged[i] - shadow[i]) * keep;
+}
+
+bool host_has_fma() {
+  static const bool has = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
+  return has;
+}
+#else
+bool host_has_fma() { return false; }
+void lerp_small_fma(float*, const float*, int64_t, float) {}
+void lerp_large_fma(float*, const float*, int64_t, float) {}
+#endif
+
 void lerp_range(float* shadow, const float* staged, int64_t begin, int64_t end, float weight, bool first) {
   if (first) {
     std::memcpy(shadow + begin, staged + begin, size_t(end - begin) * sizeof(float));
     return;
   }
+  const int64_t n = end - begin;
+  const bool fast = host_has_fma();
   if (weight < 0.5f) {
-    for (int64_t i = begin; i < end; ++i) shadow[i] = std::fmaf(weight, staged[i] - shadow[i], shadow[i]);
+    if (fast) lerp_small_fma(shadow + begin, staged + begin, n, weight);
+    else lerp_small_body(shadow + begin, staged + begin, n, weight);
   } else {
     const float keep = 1.0f - weight;
-    for (int64_t i = begin; i < end; ++i) shadow[i] = staged[i] - (staged[i] - shadow[i]) * keep;
+    if (fast) lerp_large_fma(shadow + begin, staged + begin, n, keep);
+    else lerp_large_body(shadow + begin, staged + begin, n, keep);
   }
 }
 
