@@ -47,10 +47,11 @@ class OptimizerIntegratedEMA:
         # GPU: work queued by update_param until finalize_updates
         self._copy_queue: list[tuple[Tensor, Tensor]] = []
         self._lerp_queue: list[tuple[Tensor, Tensor]] = []
-        # CPU: one pinned staging buffer, one job in flight at most
+        # CPU: one pinned staging buffer, one update in flight at most (its jobs: one per
+        # chunk of the snapshot, so the host averages chunk i while chunk i + 1 crosses the link)
         self._staged: list[tuple[Tensor, dict[str, Any]]] = []
         self._staging: Tensor | None = None
-        self._job: _native.CpuEmaJob | None = None
+        self._jobs: list[_native.CpuEmaJob] = []
         self._job_states: list[dict[str, Any]] = []
         self._snapshot_event: torch.cuda.Event | None = None
         self._copy_streams: dict[torch.device, torch.cuda.Stream] = {}
@@ -180,11 +181,31 @@ class OptimizerIntegratedEMA:
             stream = self._copy_streams[device] = torch.cuda.Stream(device=device)
         return stream
 
+    # A snapshot of at least this many elements is taken in SNAPSHOT_CHUNKS pieces.
+    SNAPSHOT_CHUNK_MIN_ELEMENTS = 1 << 24
+    SNAPSHOT_CHUNKS = 4
+
+    def _snapshot_chunks(self, items: list[tuple[int, Tensor]]) -> list[list[tuple[int, Tensor]]]:
+        """``items`` (index, parameter) cut, in order, into pieces of about equal element counts."""
+        total = sum(p.numel() for _, p in items)
+        if total < self.SNAPSHOT_CHUNK_MIN_ELEMENTS or len(items) < 2:
+            return [items]
+        target = -(-total // self.SNAPSHOT_CHUNKS)
+        chunks: list[list[tuple[int, Tensor]]] = [[]]
+        filled = 0
+        for item in items:
+            if filled >= target and len(chunks) < self.SNAPSHOT_CHUNKS:
+                chunks.append([])
+                filled = 0
+            chunks[-1].append(item)
+            filled += item[1].numel()
+        return chunks
+
     def _launch_cpu_update(self) -> None:
         staged, self._staged = self._staged, []
         if not staged:
             return
-        if self._job is not None:
+        if self._jobs:
             raise RuntimeError("CPU EMA job already pending after the pre-step wait")
         total = sum(p.numel() for p, _ in staged)
         pin = self.config.pin_memory
@@ -196,61 +217,73 @@ class OptimizerIntegratedEMA:
             offsets.append(cursor)
             state[EMA_TMP_CPU] = staging[cursor : cursor + param.numel()].view(param.shape)
             cursor += param.numel()
-        event: torch.cuda.Event | None = None
+        # (members, event) per job: the worker of a job waits for its event, then averages its members
+        pieces: list[tuple[list[int], torch.cuda.Event | None]] = []
         cuda_items = [(i, p) for i, (p, _) in enumerate(staged) if p.is_cuda]
         if cuda_items and pin:
             device = cuda_items[0][1].device
             side = self._copy_stream(device)
             side.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(side):
-                by_dtype: dict[torch.dtype, list[int]] = {}
-                for i, p in cuda_items:
-                    by_dtype.setdefault(p.dtype, []).append(i)
-                for dtype, members in by_dtype.items():
-                    sources = [staged[i][0] if staged[i][0].is_contiguous() else staged[i][0].contiguous()
-                               for i in members]
-                    if dtype not in (torch.float32, torch.float16, torch.bfloat16):
-                        sources = [s.float() for s in sources]
-                    # The kernel writes through the pinned buffer's device mapping.
-                    _native.ema_stage_pack(sources, [offsets[i] for i in members], staging)
-                    for s in sources:
-                        s.record_stream(side)
-                event = torch.cuda.Event(blocking=False)
-                event.record(side)
-            self._snapshot_event = event
+                for chunk in self._snapshot_chunks(cuda_items):
+                    by_dtype: dict[torch.dtype, list[int]] = {}
+                    for i, p in chunk:
+                        by_dtype.setdefault(p.dtype, []).append(i)
+                    for dtype, members in by_dtype.items():
+                        sources = [staged[i][0] if staged[i][0].is_contiguous() else staged[i][0].contiguous()
+                                   for i in members]
+                        if dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                            sources = [s.float() for s in sources]
+                        # The kernel writes through the pinned buffer's device mapping.
+                        _native.ema_stage_pack(sources, [offsets[i] for i in members], staging)
+                        for s in sources:
+                            s.record_stream(side)
+                    event = torch.cuda.Event(blocking=False)
+                    event.record(side)
+                    pieces.append(([i for i, _ in chunk], event))
+            self._snapshot_event = pieces[-1][1]   # the last piece is recorded after all the others
             rest = [i for i, (p, _) in enumerate(staged) if not p.is_cuda]
         else:
             rest = list(range(len(staged)))
         for i in rest:  # host parameters, or unpinned staging: plain blocking copies
             staged[i][1][EMA_TMP_CPU].copy_(staged[i][0].detach(), non_blocking=False)
-        first = [not state[EMA_INITIALIZED] for _, state in staged]
+        if rest:
+            pieces.append((rest, None))
         weight = 1.0 - (self.config.decay if self._decay_now is None else self._decay_now)
-        for _, state in staged:
-            state[EMA_EVENT] = event
-        self._job = _native.CpuEmaJob(
-            [state[EMA_SHADOW].view(-1) for _, state in staged],
-            [state[EMA_TMP_CPU].view(-1) for _, state in staged], first, weight, event, self._threads)
         self._job_states = [state for _, state in staged]
+        for members, event in pieces:
+            states = [staged[i][1] for i in members]
+            for state in states:
+                state[EMA_EVENT] = event
+            self._jobs.append(_native.CpuEmaJob(
+                [state[EMA_SHADOW].view(-1) for state in states],
+                [state[EMA_TMP_CPU].view(-1) for state in states],
+                [not state[EMA_INITIALIZED] for state in states], weight, event, self._threads))
 
     def _order_after_snapshot(self) -> None:
         """Make the device wait until the last snapshot no longer reads the live parameters."""
         event, self._snapshot_event = self._snapshot_event, None
         if event is not None:
             torch.cuda.current_stream().wait_event(event)
-        if self._job is not None and self._job.done():
+        if self._jobs and all(job.done() for job in self._jobs):
             self._finish_job()
 
     def _finish_job(self) -> None:
-        job, self._job = self._job, None
-        if job is None:
+        """Wait for every job of the update in flight; the first failure is re-raised after all are closed."""
+        jobs, self._jobs = self._jobs, []
+        if not jobs:
             return
         states, self._job_states = self._job_states, []
-        try:
-            job.wait_update()
-        except Exception as exc:
-            raise RuntimeError("Asynchronous CPU EMA update failed") from exc
-        finally:
-            job.close()
+        failure: Exception | None = None
+        for job in jobs:
+            try:
+                job.wait_update()
+            except Exception as exc:  # noqa: BLE001 - re-raised below with the reference's message
+                failure = failure or exc
+            finally:
+                job.close()
+        if failure is not None:
+            raise RuntimeError("Asynchronous CPU EMA update failed") from failure
         for state in states:
             state[EMA_INITIALIZED] = True
             state[EMA_PENDING] = False

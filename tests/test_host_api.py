@@ -168,9 +168,30 @@ def test_cpu_ema_worker_failure_reaches_the_waiting_thread() -> None:
     assert job.done()
 
     tracker = OptimizerIntegratedEMA.__new__(OptimizerIntegratedEMA)
-    tracker._job = _native.CpuEmaJob([shadow], [Missing()], [False], 0.5, None, 2)
-    tracker._job_states = [{}]
+    good = torch.ones(16)
+    tracker._jobs = [_native.CpuEmaJob([shadow], [Missing()], [False], 0.5, None, 2),
+                     _native.CpuEmaJob([good], [torch.zeros(16)], [False], 0.5, None, 2)]
+    tracker._job_states = [{}, {}]
     with pytest.raises(RuntimeError, match="Asynchronous CPU EMA update failed"):
         tracker._finish_job()
-    assert tracker._job is None
+    assert tracker._jobs == []
+    assert torch.equal(good, torch.full((16,), 0.5))   # the other job of the update still ran to its end
     assert torch.equal(shadow, torch.zeros(16))
+
+
+def test_snapshot_chunks_keep_order_and_balance() -> None:
+    """The CPU EMA cuts a large snapshot into pieces so that the host averages one piece while the
+    next one crosses the link: every parameter lands in exactly one piece, in order."""
+    from dionw_b200.ema.tracker import OptimizerIntegratedEMA
+
+    tracker = OptimizerIntegratedEMA.__new__(OptimizerIntegratedEMA)
+    small = [(i, torch.empty(1000, device="meta")) for i in range(5)]
+    assert tracker._snapshot_chunks(small) == [small]
+    sizes = [1 << 22] * 9 + [1 << 25, 4096, 1 << 23]
+    items = [(i, torch.empty(n, device="meta")) for i, n in enumerate(sizes)]
+    chunks = tracker._snapshot_chunks(items)
+    assert 1 < len(chunks) <= tracker.SNAPSHOT_CHUNKS
+    assert [i for chunk in chunks for i, _ in chunk] == list(range(len(sizes)))
+    assert all(chunk for chunk in chunks)
+    one = [(0, torch.empty(1 << 26, device="meta"))]
+    assert tracker._snapshot_chunks(one) == [one]
