@@ -564,8 +564,6 @@ def run_ns_microbench(args) -> None:
         del x, packed, scratch, work, y
         torch.cuda.empty_cache()
     launches = _native.launch_count() - launches_before
-    if replay:   # a replayed step executes the kernels of its recording without passing the library's counter
-        launches += (optimizer.graph_replays - replays_before) * optimizer.graph_kernels
     clocks = sampler.stop()
     big = rows_out[-1]
     total_flops = sum(NS_BATCH * flops_newton_schulz(m, n) for m, n in NS_SHAPES)
@@ -752,7 +750,11 @@ def run_gpu_arm(args) -> None:
         optimizer.step()
     barrier()
 
-    # ---- timed region: exactly K steps, device time, max over ranks
+    # ---- timed region: exactly K steps, device time, max over ranks.  Then, right after it (the GPU
+    # is still in the same power and clock state), K more steps with every stage of every run bracketed
+    # by CUDA events on the launching stream: the per-stage figures describe the steady state the
+    # headline was measured in, and the event records stay out of the headline.  A replayed step
+    # cannot carry events: its stages are timed below, in steps run as launches.
     launches_before = _native.launch_count()
     replays_before = optimizer.graph_replays if replay else 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -766,6 +768,17 @@ def run_gpu_arm(args) -> None:
     launches = _native.launch_count() - launches_before
     if replay:   # a replayed step executes the kernels of its recording without passing the library's counter
         launches += (optimizer.graph_replays - replays_before) * optimizer.graph_kernels
+    stages: dict[str, float] = {}
+    whole_ms = None
+    if not replay:
+        timer.enabled = True
+        for _ in range(args.steps):
+            with timer("whole_step"):
+                optimizer.step()
+        timer.enabled = False
+        barrier()
+        stages = {k: v / args.steps for k, v in timer.collect().items()}
+        whole_ms = stages.pop("whole_step", None)   # the same steps, bracketed once: shows what lies between the stages
     extra_deadline = time.time() + 4.0
     while True:
         need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
@@ -784,18 +797,18 @@ def run_gpu_arm(args) -> None:
         total_ms = float(t)
     ms_per_step = total_ms / args.steps
 
-    # ---- per-stage device time (separate steps so the events do not sit in the timed region)
-    timer.enabled = True
-    _matrix_step.STAGE_HOOK = timer
-    stage_steps = max(1, min(3, args.steps))
-    for _ in range(stage_steps):
-        with timer("whole_step"):
-            optimizer.step()
-    stages = {k: v / stage_steps for k, v in timer.collect().items()}
-    timer.enabled = False
+    # ---- per-stage device time of a replayed step: separate steps, run as launches with the hook installed
     if replay:
+        timer.enabled = True
+        _matrix_step.STAGE_HOOK = timer
+        stage_steps = max(1, min(3, args.steps))
+        for _ in range(stage_steps):
+            with timer("whole_step"):
+                optimizer.step()
+        stages = {k: v / stage_steps for k, v in timer.collect().items()}
+        timer.enabled = False
         _matrix_step.STAGE_HOOK = None
-    whole_ms = stages.pop("whole_step", None)   # the same steps, bracketed once: shows what lies between the stages
+        whole_ms = stages.pop("whole_step", None)
 
     # ---- host dispatch: wall time for step() to return with the GPU idle at the start and
     # no synchronize inside (one step's launches fit the driver's launch queue)
