@@ -879,6 +879,9 @@ def run_gpu_arm(args) -> None:
     }
     if "ema" in stages:
         stage_report["ema"] = {"ms": stages["ema"], "GB/s": gbs("bytes_ema", "ema", share)}
+    for entry in stage_report.values():   # each HBM-bound stage against the measured copy bandwidth
+        if isinstance(entry, dict) and entry.get("GB/s"):
+            entry["frac_of_hbm_peak"] = entry["GB/s"] / peaks["hbm_gbs"]
     if "ema_stage" in stages:
         # fp32 snapshot of every parameter written by one kernel into pinned host memory: bound by
         # the host link (PCIe), not HBM; the worker thread's lerp on the host follows it
