@@ -245,25 +245,55 @@ select_rows_kernel(const float* __restrict__ scores, const float* __restrict__ s
   const float* sc = scores + b * rows;
   const float* ss = sumsq + b * rows;
 
+  const int warp = tid >> 5, lane = tid & 31;
   uint32_t prefix = 0, mask = 0, remaining = uint32_t(k);
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (int r = tid; r < rows; r += kSelectThreads) {
-      const uint32_t key = order_key(sc[r]);
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    // Scores of one block share sign and exponent, so in the first passes nearly every key
+    // falls into one bin: the lanes of a warp that hit the same bin add once, together.
+    for (int start = 0; start < rows; start += kSelectThreads) {
+      const int r = start + tid;
+      uint32_t bin = 256;   // not a candidate (or past the end)
+      if (r < rows) {
+        const uint32_t key = order_key(sc[r]);
+        if ((key & mask) == prefix) bin = (key >> shift) & 255u;
+      }
+      const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+      if (bin < 256 && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], uint32_t(__popc(peers)));
     }
     __syncthreads();
-    if (tid == 0) {
-      uint32_t above = 0;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        if (above + hist[bin] >= remaining) break;
-        above += hist[bin];
+    // The highest bin whose count, added to the counts above it, reaches `remaining`: lane l of
+    // warp 0 holds bins 8l..8l+7, a suffix sum over the lanes finds the lane, which finds the bin.
+    if (warp == 0) {
+      uint32_t cnt[8], own = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cnt[i] = hist[lane * 8 + i];
+        own += cnt[i];
       }
-      s_prefix = prefix | (uint32_t(bin) << shift);
-      s_remaining = remaining - above;
+      uint32_t incl = own;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t v = __shfl_down_sync(0xffffffffu, incl, d);
+        if (lane + d < 32) incl += v;
+      }
+      uint32_t above = incl - own;   // candidates in the bins of higher lanes
+      if (above < remaining && remaining <= incl) {
+        int found = 0;
+        bool open = true;
+#pragma unroll
+        for (int i = 7; i > 0; --i) {
+          if (open && above + cnt[i] >= remaining) {
+            found = i;
+            open = false;
+          }
+          if (open) above += cnt[i];
+        }
+        s_prefix = prefix | (uint32_t(lane * 8 + found) << shift);
+        s_remaining = remaining - above;
+      }
     }
     __syncthreads();
     prefix = s_prefix;
@@ -276,7 +306,6 @@ select_rows_kernel(const float* __restrict__ scores, const float* __restrict__ s
 
   uint32_t base_gt = 0, base_eq = 0;
   float local = 0.0f;
-  const int warp = tid >> 5, lane = tid & 31;
   for (int start = 0; start < rows; start += kSelectThreads) {
     const int r = start + tid;
     uint32_t key = 0;

@@ -94,8 +94,9 @@ class OptimizerIntegratedEMA:
             self._due = since > 0 and since % every == 0
         decay = cfg.decay_at_step(self._step_count)
         self._decay_now = decay**every if self._due and not self._reseed else None
-        if self._due and not self._on_gpu:
-            self._finish_job()
+        # The previous CPU update is awaited at this step's first ``update_param``, not here: the
+        # optimizer's own step, which runs in between, touches neither the shadows nor the staging
+        # buffer, so its GPU work overlaps the tail of that update.
 
     def should_update_this_step(self) -> bool:
         """Whether this step updates the shadows."""
@@ -108,6 +109,8 @@ class OptimizerIntegratedEMA:
         with self._profile_region(_STAGE_REGION):
             if not self._due or param not in self.optimizer.state:
                 return
+            if self._jobs:   # CPU: the update in flight owns the shadows and the staging buffer
+                self._finish_job()
             state = self.optimizer.state[param]
             if EMA_SHADOW not in state:
                 self._new_shadow(param, state)
