@@ -40,6 +40,8 @@ CONFIGS = {
     # name: (layers, d_model, d_kv, d_ff, vocab)
     "llama3-8b": (32, 4096, 1024, 14336, 128256),
     "llama3-8b-2layers": (2, 4096, 1024, 14336, 16032),
+    # the matrix blocks one rank of eight owns at the full configuration (8 gate/up, 8 q/o, 8 k/v, 4 down)
+    "llama3-8b-4layers": (4, 4096, 1024, 14336, 16032),
     "tiny": (2, 1024, 256, 3584, 4096),
     # 20-layer slice of the Llama-3-70B shapes, embedding only, GPU EMA (decay 0.9999): 8 GPUs
     "llama3-70b-20layers": (20, 8192, 1024, 28672, 128256),
@@ -687,6 +689,8 @@ def run_gpu_arm(args) -> None:
             optimizer.overlap_apply = True
         if args.round_elements:
             optimizer.round_elements = args.round_elements
+        if args.adamw_first:
+            optimizer.adamw_first = True
     else:
         optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
     if args.no_overlap:
@@ -897,7 +901,8 @@ def run_gpu_arm(args) -> None:
                    "lr": LR, "weight_decay": WEIGHT_DECAY, "l2": "working set >> L2 (126 MB), no flush needed",
                    "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)",
                    "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
-                                     "round_elements": int(optimizer.round_elements)} if distributed else None),
+                                     "round_elements": int(optimizer.round_elements),
+                                     "adamw_first": bool(optimizer.adamw_first)} if distributed else None),
                    "ema": (None if ema is None else
                            f"{ema_kind.upper()} shadows, decay 0.9999, every step"
                            + (" (pinned host shadows, one snapshot kernel + host worker thread per step; the "
@@ -942,6 +947,8 @@ def main() -> None:
     parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--adamw-first", action="store_true",
+                        help="sharded step: AdamW and its all-gathers before the first round (for comparison)")
     parser.add_argument("--ema", choices=("config", "none", "gpu", "cpu"), default="config",
                         help="EMA of every parameter: 'config' = GPU shadows for the 70B-shaped configs, none otherwise")
     parser.add_argument("--graph-replay", action="store_true",
