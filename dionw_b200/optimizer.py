@@ -15,6 +15,7 @@ a CUDA device.
 
 from __future__ import annotations
 
+import warnings
 from collections.abc import Callable, Iterable
 from typing import Any
 
@@ -25,7 +26,7 @@ from torch.optim import Optimizer
 from dionw_b200._adamw import adamw_step, init_adamw_state
 from dionw_b200._buckets import Bucket, block_shape, build_buckets
 from dionw_b200._keys import (
-    EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, NEWTON_SCHULZ_KEY,
+    ADAMW_STEP_STATE, EXP_AVG_SQ_STATE, EXP_AVG_STATE, FRACTION_KEY, MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, NEWTON_SCHULZ_KEY,
     NUM_HEADS_KEY, ROUTE_KEY, ROW_NORMALIZATION_KEY, STRUCTURAL_KEYS,
 )
 from dionw_b200._matrix_step import (
@@ -167,6 +168,7 @@ class _DionCore(Optimizer):
         _require_group({**self.defaults, **group})
         super().add_param_group(group)
         self._buckets = None
+        self._graph = self._graph_warm = None
         # AdamW state exists from the start so that an integrated EMA tracks every
         # parameter, also one that never gets a gradient; matrix state appears with
         # the buckets at the first step.
@@ -211,6 +213,7 @@ class _DionCore(Optimizer):
         _require_same_structure(saved, self.param_groups)
         super().load_state_dict({**state_dict, "param_groups": saved})
         self._buckets = None
+        self._graph = self._graph_warm = None
 
     @torch.no_grad()
     def step(self, closure: Callable[[], float] | None = None) -> float | None:
@@ -235,7 +238,7 @@ class _DionCore(Optimizer):
         self._step_adamw_groups()
 
     # Optional replay of the step from a CUDA graph.  The reference measures 7-17 ms of host
-    # dispatch per step of its own (README.md:514-516, bench/host_dispatch.py:28-56); here a step
+    # dispatch per step of its own (README.md:514-516 and bench/host_dispatch.py:28-56 there); here a step
     # is a few hundred launches through ctypes.  With ``graph_replay = True`` the first step of a
     # configuration runs as launches (it creates state, grows the scratch arenas and does the
     # one-time device set-up), the second is recorded on a capture stream and replayed, and every
@@ -280,7 +283,15 @@ class _DionCore(Optimizer):
         for group in self.param_groups:
             parts.append((float(group["lr"]), float(group["weight_decay"]), float(group[MOMENTUM_KEY]),
                           float(group[MUON_BETA2_KEY]), tuple(map(float, group["betas"])), float(group["eps"])))
-            parts.append(tuple((p.data_ptr(), p.grad.data_ptr()) for p in group["params"] if p.grad is not None))
+            adamw = RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                parts.append((p.data_ptr(), p.grad.data_ptr()))
+                if adamw:   # a loaded checkpoint replaces these tensors
+                    entry = self.state[p]
+                    parts.append(tuple(entry[key].data_ptr() for key in (EXP_AVG_STATE, EXP_AVG_SQ_STATE, ADAMW_STEP_STATE)
+                                       if key in entry))
         for bucket, run in runs:
             parts.append((bucket.momentum.data_ptr(), bucket.variance.data_ptr(), tuple(run)))
         return tuple(parts)
@@ -303,8 +314,15 @@ class _DionCore(Optimizer):
 
         graph = torch.cuda.CUDAGraph()
         before = _native.launch_count()
-        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self._step_in_sequence(runs)
+        except Exception as exc:  # noqa: BLE001 - a capture executes nothing: the step can still run as launches
+            warnings.warn(f"Dion.graph_replay: recording the step failed ({exc!r}); stepping as launches from now on",
+                          RuntimeWarning, stacklevel=3)
+            self._graph_recordings = self.GRAPH_RECORDINGS_MAX
             self._step_in_sequence(runs)
+            return
         self.graph_kernels = _native.launch_count() - before
         graph.replay()
         self.graph_replays += 1

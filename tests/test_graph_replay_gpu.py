@@ -106,3 +106,32 @@ def test_gradients_that_move_fall_back_to_launches() -> None:
             assert torch.equal(pa, pb), step
     assert opt_a._graph_recordings == 1 and opt_a._graph is None
     _same_state(opt_a, opt_b)
+
+
+def test_a_loaded_checkpoint_drops_the_recording() -> None:
+    """``load_state_dict`` replaces the state tensors a recording points at: the recording goes,
+    the next steps run as launches, are recorded anew and keep matching the unrecorded optimizer."""
+    import io
+
+    (net_a, opt_a), (net_b, opt_b) = _build(True, ema=False), _build(False, ema=False)
+    gen = torch.Generator(device=DEV).manual_seed(4)
+    for _ in range(3):
+        _fill_grads(net_a, net_b, gen)
+        opt_a.step()
+        opt_b.step()
+    assert opt_a._graph is not None
+    buffer = io.BytesIO()
+    torch.save(opt_b.state_dict(), buffer)
+    for opt in (opt_a, opt_b):
+        buffer.seek(0)
+        opt.load_state_dict(torch.load(buffer, weights_only=False))
+    assert opt_a._graph is None
+    for step in range(4):
+        _fill_grads(net_a, net_b, gen)
+        opt_a.step()
+        opt_b.step()
+        torch.cuda.synchronize()
+        for pa, pb in zip(net_a.parameters(), net_b.parameters()):
+            assert torch.equal(pa, pb), step
+    assert opt_a._graph is not None and opt_a._graph_recordings == 2
+    _same_state(opt_a, opt_b)
