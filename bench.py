@@ -9,10 +9,18 @@ gradients stay the same tensors across timed steps, as in the reference's own
 benchmark (bench/optimizer_step.py:91-96 there).  Working set (~100 GB) is far
 larger than L2, so nothing is flushed between steps.
 
-Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU oracle
+Prints ONE JSON line (rank 0).  ``value`` is the device time of K steps; the
+``stages`` come from K further steps run right after them with every stage
+bracketed by CUDA events; ``e2e`` copies every gradient from pinned host memory
+each step.  ``--impl reference`` times the CPU oracle
 (``oracle/dion_oracle.py``, the restatement of the reference's step pinned by
 its fixtures) on the host cores instead, on a bounded sample of the same
-workload.
+workload (one whole layer, scaled by the layer count).
+
+Other workloads: ``--config gpt2-small`` (config 2), ``--config single-1024x4096``
+(config 1), ``--config llama3-70b-20layers`` (config 5, 8 GPUs), ``--config gram-ns``
+(config 4, the Newton-Schulz microbenchmark), ``--config gemm-sustained`` (the GEMM
+against cuBLAS under the power cap); ``--ema cpu|gpu``, ``--graph-replay``.
 """
 
 from __future__ import annotations
