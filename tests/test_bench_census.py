@@ -49,3 +49,12 @@ def test_single_matrix_and_70b_slice_census() -> None:
     big = bench.census(_groups("llama3-70b-20layers"))
     assert big["ns_flops"] == pytest.approx(474.5e12, rel=2e-3)
     assert big["matrix_elements"] + big["adamw_elements"] == pytest.approx(18.16e9, rel=2e-3)
+
+
+def test_cpu_arm_runs_the_single_matrix_workload_whole() -> None:
+    """The reference arm's sample on the one workload it runs unscaled (config 1)."""
+    base = bench.cpu_sample_step("single-1024x4096", steps=2, warmup=1)
+    assert base["kind"] == "port" and base["unit"] == "ms" and base["cores"] >= 1
+    assert 0.0 < base["sample_ms"] <= base["value"] * 1.0001
+    assert base["value"] == pytest.approx(base["sample_ms"], rel=1e-6)   # scale factors are 1
+    assert "whole workload" in base["sample"]
