@@ -212,6 +212,7 @@ class StageTimer:
 
     def __init__(self) -> None:
         self.events: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+        self.blocks: dict[str, int] = {}
         self.enabled = False
 
     @contextlib.contextmanager
@@ -224,6 +225,12 @@ class StageTimer:
         yield
         end.record()
         self.events.append((name, start, end))
+        if name == "newton_schulz":   # also per operand shape: blocks x selected rows x cols of the run
+            from dionw_b200 import _matrix_step
+
+            count, _, k, cols = _matrix_step.CURRENT_RUN or (0, 0, 0, 0)
+            self.events.append((f"ns:{k}x{cols}", start, end))
+            self.blocks[f"ns:{k}x{cols}"] = self.blocks.get(f"ns:{k}x{cols}", 0) + count
 
     def collect(self) -> dict[str, float]:
         torch.cuda.synchronize()
@@ -280,6 +287,22 @@ class ClockSampler:
         loaded = [v for v in sm if v > 0.5 * max(sm)] or sm
         return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": float(rows[0][1]), "samples": len(rows),
                 "power_w_max": max(float(r[2]) for r in rows), "reasons": reasons}
+
+
+def split_ns_shapes(stages: dict[str, float], blocks: dict[str, int], steps: int) -> list[dict]:
+    """Takes the per-shape Newton-Schulz entries (``ns:<m>x<n>``) out of ``stages`` and returns them as
+    rows: operand shape, blocks and milliseconds per step on this rank, executed TFLOP/s."""
+    rows = []
+    for key in sorted(k for k in stages if k.startswith("ns:")):
+        ms = stages.pop(key)
+        k, cols = (int(v) for v in key[3:].split("x"))
+        m, n = min(k, cols), max(k, cols)
+        count = blocks.get(key, 0) / max(1, steps)
+        rows.append({"operand": [m, n], "blocks": count, "ms": ms,
+                     "executed_TFLOP/s": count * flops_newton_schulz_executed(m, n) / ms / 1e9 if ms else None,
+                     "algorithmic_TFLOP/s": count * flops_newton_schulz(m, n) / ms / 1e9 if ms else None})
+    blocks.clear()
+    return rows
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -653,6 +676,72 @@ def run_gemm_sustained(args) -> None:
 
 
 # ---------------------------------------------------------------------------
+# correctness of the sharded step, checked inside the distributed run (outside the timed region)
+# ---------------------------------------------------------------------------
+def sharded_parity(device, rank: int, dist) -> dict:
+    """Three steps of ``ShardedDion`` on every rank and of single-GPU ``Dion`` on rank 0, on the
+    ``tiny`` parameter set (blocks that select rows and blocks that do not, an AdamW table large
+    enough to be cut into per-rank ranges) from identical seeds.  Reports whether the replicas
+    hold identical weights, how far rank 0's weights are from the single-GPU ones (the design
+    is bit-identical: 0.0 expected) and the same for the gathered ``state_dict()``."""
+    import dionw_b200 as dionw
+    from dionw_b200 import _workspace
+    from dionw_b200.distributed import ShardedDion
+
+    def build():
+        model = build_model("tiny", device)
+        model.init_(seed=7)
+        routes = {model.lm_head.weight: dionw.Route(dionw.RouteKind.ADAMW)}
+        groups, _ = dionw.param_groups(model, routes=routes)
+        return model, groups
+
+    model, groups = build()
+    sharded = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+    single_model = single = None
+    if rank == 0:
+        single_model, single_groups = build()
+        single = dionw.Dion(single_groups, lr=LR, weight_decay=WEIGHT_DECAY)
+    steps = 3
+    for step in range(steps):
+        gen = torch.Generator(device=device).manual_seed(100 + step)
+        grads = [torch.empty_like(p).normal_(0.0, 1e-3, generator=gen) for p in model.parameters()]
+        for p, g in zip(model.parameters(), grads):
+            p.grad = g
+        sharded.step()
+        if single is not None:
+            for p, g in zip(single_model.parameters(), grads):
+                p.grad = g.clone()
+            single.step()
+    torch.cuda.synchronize()
+    spread = torch.zeros((), device=device)
+    for p in model.parameters():
+        reference = p.detach().clone()
+        dist.broadcast(reference, src=0)
+        spread = torch.maximum(spread, (p.detach() - reference).abs().max())
+    dist.all_reduce(spread, op=dist.ReduceOp.MAX)
+    gathered = sharded.state_dict()   # a collective call: every rank makes it
+    result = {"workload": "tiny parameter set (2 layers, d = 1024), 3 steps, identical seeds", "steps": steps,
+              "replicas_identical": bool(float(spread) == 0.0), "replicas_max_abs": float(spread)}
+    if single is not None:
+        worst = max(float((a.detach() - b.detach()).abs().max())
+                    for a, b in zip(model.parameters(), single_model.parameters()))
+        want = single.state_dict()
+        state_worst, compared = 0.0, 0
+        for index, entry in want["state"].items():
+            for key, value in entry.items():
+                if isinstance(value, torch.Tensor):
+                    got = gathered["state"][index][key]
+                    state_worst = max(state_worst, float((got.float() - value.float()).abs().max()))
+                    compared += 1
+        result.update({"vs_single_gpu_max_abs": worst, "state_dict_vs_single_gpu_max_abs": state_worst,
+                       "state_tensors_compared": compared})
+    del sharded, single, model, single_model, gathered
+    _workspace.release()
+    torch.cuda.empty_cache()
+    return result
+
+
+# ---------------------------------------------------------------------------
 # the GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu_arm(args) -> None:
@@ -664,12 +753,17 @@ def run_gpu_arm(args) -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    distributed = world > 1
+    distributed = world > 1 or args.sharded
     if distributed:
         import torch.distributed as dist
 
+        if world == 1:   # --sharded on one GPU: the sharded step's machinery with a group of one
+            for key, value in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533"), ("RANK", "0"),
+                               ("WORLD_SIZE", "1")):
+                os.environ.setdefault(key, value)
         dist.init_process_group("nccl", device_id=device)
     _native.library()
+    parity = sharded_parity(device, rank, dist) if distributed and not args.no_parity else None
 
     layers, d, dkv, dff, vocab = CONFIGS[args.config]
     weights_bytes = 4.0 * (layers * (2 * d * d + 2 * d * dkv + 3 * d * dff)
@@ -699,6 +793,8 @@ def run_gpu_arm(args) -> None:
             optimizer.round_elements = args.round_elements
         if args.adamw_first:
             optimizer.adamw_first = True
+        if args.apply_warps:
+            optimizer.apply_warps = args.apply_warps
     else:
         optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
     if args.no_overlap:
@@ -729,9 +825,9 @@ def run_gpu_arm(args) -> None:
         _matrix_step.STAGE_HOOK = timer
     real_adamw = _adamw.adamw_step
 
-    def timed_adamw(group, state):
+    def timed_adamw(group, state, **kwargs):
         with timer("adamw"):
-            real_adamw(group, state)
+            real_adamw(group, state, **kwargs)
 
     import dionw_b200.optimizer as optimizer_module
     optimizer_module.adamw_step = timed_adamw
@@ -781,6 +877,7 @@ def run_gpu_arm(args) -> None:
     if replay:   # a replayed step executes the kernels of its recording without passing the library's counter
         launches += (optimizer.graph_replays - replays_before) * optimizer.graph_kernels
     stages: dict[str, float] = {}
+    ns_by_shape: list[dict] = []
     whole_ms = None
     if not replay:
         timer.enabled = True
@@ -791,6 +888,7 @@ def run_gpu_arm(args) -> None:
         barrier()
         stages = {k: v / args.steps for k, v in timer.collect().items()}
         whole_ms = stages.pop("whole_step", None)   # the same steps, bracketed once: shows what lies between the stages
+        ns_by_shape = split_ns_shapes(stages, timer.blocks, args.steps)
     extra_deadline = time.time() + 4.0
     while True:
         need = rank == 0 and sampler.samples() < 10 and time.time() < extra_deadline
@@ -821,6 +919,7 @@ def run_gpu_arm(args) -> None:
         timer.enabled = False
         _matrix_step.STAGE_HOOK = None
         whole_ms = stages.pop("whole_step", None)
+        ns_by_shape = split_ns_shapes(stages, timer.blocks, stage_steps)
 
     # ---- host dispatch: wall time for step() to return with the GPU idle at the start and
     # no synchronize inside (one step's launches fit the driver's launch queue)
@@ -872,6 +971,7 @@ def run_gpu_arm(args) -> None:
     share = 1.0 / world  # matrix blocks and the AdamW space are sharded evenly by cost
     ns_ms = stages.get("newton_schulz", 0.0)
     ns_tflops = work["ns_flops"] * share / ns_ms / 1e9 if ns_ms else None
+    ns_exec_tflops = work["ns_flops_executed"] * share / ns_ms / 1e9 if ns_ms else None
     peak_tf = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
 
     def gbs(key: str, stage: str, scale: float = 1.0) -> float | None:
@@ -882,7 +982,7 @@ def run_gpu_arm(args) -> None:
         "accumulate": {"ms": stages.get("accumulate"), "GB/s": gbs("bytes_accumulate", "accumulate", share)},
         "select": {"ms": stages.get("select")},
         "pack": {"ms": stages.get("pack"), "GB/s": gbs("bytes_pack", "pack", share)},
-        "newton_schulz": {"ms": ns_ms, "TFLOP/s": ns_tflops},
+        "newton_schulz": {"ms": ns_ms, "TFLOP/s": ns_tflops, "by_operand": ns_by_shape},
         "finish": {"ms": stages.get("finish"), "GB/s": gbs("bytes_finish", "finish", share)},
         "apply": {"ms": stages.get("apply"), "GB/s": gbs("bytes_apply", "apply")},
         "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
@@ -909,6 +1009,7 @@ def run_gpu_arm(args) -> None:
                    "lr": LR, "weight_decay": WEIGHT_DECAY, "l2": "working set >> L2 (126 MB), no flush needed",
                    "parallelism": f"blocks sharded by Newton-Schulz cost over {world} GPU(s)",
                    "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
+                                     "apply_warps": int(optimizer.apply_warps),
                                      "round_elements": int(optimizer.round_elements),
                                      "adamw_first": bool(optimizer.adamw_first)} if distributed else None),
                    "ema": (None if ema is None else
@@ -921,19 +1022,21 @@ def run_gpu_arm(args) -> None:
                                  "beside the state)" if shared_grads else "one tensor per parameter")},
         "roofline": {
             "kernel": "gemm2_kernel (all Newton-Schulz products of a step)",
-            "bound": "tensor", "achieved": ns_tflops, "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": ns_tflops / peak_tf if ns_tflops else None, "traffic": work["ns_traffic"] * share,
+            "bound": "tensor", "achieved": ns_exec_tflops, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": ns_exec_tflops / peak_tf if ns_exec_tflops else None, "traffic": work["ns_traffic"] * share,
+            "achieved_kind": ("FLOPs the kernels execute, 2(3m^2n + 7m^3) per m x n operand (the products Q Z, G Z and "
+                              "Z RZ run on the lower-triangle schedule), / the summed CUDA-event time of the stage"),
             "traffic_kind": ("DRAM bytes of all gemm2_kernel launches of one step on this rank: the operand census "
                              "of the products, calibrated x1.06 on an ncu capture of the 18 products of four "
                              "3584x4096 blocks and scaled by blocks (traffic grows with the blocks processed)"),
             "peak_kind": f"{peaks_kind} bf16 cuBLAS, sustained (the kernel is timed inside the step)",
-            "flops_per_step": work["ns_flops"] * share,
-            "executed": {"TFLOP/s": work["ns_flops_executed"] * share / ns_ms / 1e9 if ns_ms else None,
-                         "frac": work["ns_flops_executed"] * share / ns_ms / 1e9 / peak_tf if ns_ms else None,
-                         "note": "achieved counts the algorithmic census 2(3m^2n + 11.5m^3) per block; the kernels "
-                                 "execute 2(3m^2n + 7m^3) because three more products per iteration are mirrored"},
+            "flops_per_step": work["ns_flops_executed"] * share,
+            "algorithmic": {"TFLOP/s": ns_tflops, "flops_per_step": work["ns_flops"] * share,
+                            "note": "the reference's product census 2(3m^2n + 11.5m^3) per operand / the same time: "
+                                    "an effective rate, not comparable with a hardware peak"},
         },
         "stages": stage_report,
+        "parity": parity,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
                 "steps": e2e_steps},
@@ -963,6 +1066,11 @@ def main() -> None:
                         help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
                              "counts only the steps that ran as launches")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
+    parser.add_argument("--sharded", action="store_true",
+                        help="one GPU: step with ShardedDion in a process group of one (its rounds, streams and "
+                             "single-launch weight update) instead of Dion")
+    parser.add_argument("--no-parity", action="store_true", help="sharded step: skip the correctness check before the run")
+    parser.add_argument("--apply-warps", type=int, default=0, help="sharded step with --overlap-apply: warps per CTA of the weight update")
     parser.add_argument("--overlap-apply", action="store_true",
                         help="sharded step: weight update of a round on a side stream beside the next round")
     args = parser.parse_args()

@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+from collections.abc import Callable
 from typing import Any
 
 import torch
@@ -18,11 +19,21 @@ def init_adamw_state(param: Tensor, state: dict[str, Any]) -> None:
     state[ADAMW_STEP_STATE] = torch.zeros((), dtype=torch.float32, device=param.device)
 
 
-def adamw_step(group: dict[str, Any], state: ParamState) -> None:
-    """One decoupled-decay AdamW step for the group's parameters that have gradients."""
+def adamw_step(group: dict[str, Any], state: ParamState,
+               hyper: Callable[[torch.device], Tensor | None] | None = None) -> None:
+    """One decoupled-decay AdamW step for the group's parameters that have gradients.
+
+    ``hyper(device)`` gives the two-element fp32 device tensor ``{lr, weight_decay}`` the kernel reads
+    instead of the host values (so a scheduled learning rate changes no launch), or None."""
     params = [p for p in group["params"] if p.grad is not None]
     if not params:
         return
+    devices = {p.device for p in params}
+    if len(devices) > 1:   # one launch per device, each with that device current
+        for device in sorted(devices, key=lambda d: d.index or 0):
+            adamw_step({**group, "params": [p for p in params if p.device == device]}, state, hyper)
+        return
+    device = params[0].device
     fixups: list[tuple[Tensor, Tensor]] = []
     p_list, g_list, m_list, v_list, s_list = [], [], [], [], []
     for param in params:
@@ -45,9 +56,11 @@ def adamw_step(group: dict[str, Any], state: ParamState) -> None:
         v_list.append(entry[EXP_AVG_SQ_STATE])
         s_list.append(entry[ADAMW_STEP_STATE])
     beta1, beta2 = group["betas"]
-    _native.adamw_multi(
-        p_list, g_list, m_list, v_list, s_list, lr=float(group["lr"]), beta1=float(beta1), beta2=float(beta2),
-        weight_decay=float(group["weight_decay"]), eps=float(group["eps"]),
-    )
+    with torch.cuda.device(device):
+        _native.adamw_multi(
+            p_list, g_list, m_list, v_list, s_list, lr=float(group["lr"]), beta1=float(beta1), beta2=float(beta2),
+            weight_decay=float(group["weight_decay"]), eps=float(group["eps"]),
+            hyper_device=None if hyper is None else hyper(device),
+        )
     for param, packed in fixups:
         param.copy_(packed)

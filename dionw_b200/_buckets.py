@@ -33,7 +33,12 @@ class Bucket:
 
     ``slices[i]`` is the block range of ``params[i]``; ``selected_rows`` is
     ``min(rows, ceil(fraction * rows))``; ``step_scale`` is the signed step size
-    of the last run (a host float here: it travels as a kernel argument).
+    of the last run as a host float.  ``step_device`` and ``decay_device`` are
+    one-element fp32 views of the optimizer's device table of step scalars
+    (``-step_size`` of this bucket, ``1 - lr * weight_decay`` of its group), the
+    counterpart of the 0-d ``step_scale`` tensor at src/dionw/_buckets.py:57-58:
+    kernels read them from there, so a changed learning rate changes no launch.
+    None (a bucket built by hand) makes the kernels take the host values.
     """
 
     group_index: int
@@ -46,6 +51,8 @@ class Bucket:
     momentum: Tensor
     variance: Tensor
     step_scale: float = 0.0
+    step_device: Tensor | None = None
+    decay_device: Tensor | None = None
 
     def run_blocks(self, positions: Sequence[int]) -> slice:
         """Block range covered by consecutive parameters ``positions``."""

@@ -31,7 +31,7 @@ from dionw_b200._keys import MOMENTUM_FORM_KEY, MOMENTUM_KEY, MUON_BETA2_KEY, RO
 from dionw_b200.matrix_update import MomentumForm, RowNormalization
 from dionw_b200.newton_schulz import NativeOrthogonalizer, padded, run_iteration
 
-__all__ = ["MAX_RUN_ELEMENTS", "apply_result", "open_run", "prepare_run", "run_core", "run_elements",
+__all__ = ["MAX_RUN_ELEMENTS", "apply_result", "apply_results", "open_run", "prepare_run", "run_core", "run_elements",
            "run_front", "step_run"]
 
 ADAMW_UPDATE_RMS = 0.2        # update RMS of AdamW that matrix steps are matched to
@@ -47,6 +47,9 @@ MAX_RUN_ELEMENTS = 2**28
 # "newton_schulz", "finish", "apply").  The benchmark uses it to bracket stages
 # with CUDA events; None costs nothing.
 STAGE_HOOK: Callable[[str], AbstractContextManager[object]] | None = None
+# ``(blocks, rows, selected rows, cols)`` of the run whose stages are being entered, for an observer
+# that wants its figures per shape.
+CURRENT_RUN: tuple[int, int, int, int] | None = None
 
 
 def _stage(name: str) -> AbstractContextManager[object]:
@@ -85,6 +88,7 @@ class RunResult:
     rowmap: Tensor | None
     denom: Tensor
     scale: Tensor
+    decay_device: Tensor | None = None   # 1 - lr * weight_decay in device memory (None: the host value is used)
 
 
 def exchange_plan(count: int, rows: int, k: int, cols: int, selecting: bool) -> _workspace.Plan:
@@ -167,8 +171,13 @@ def open_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], ar
         "sumsq": ((count, rows), torch.float32),
         "index": ((count, k), torch.int32),
         "frob": ((count,), torch.float32),
-        "rowsq": ((count * k,), torch.float32),
     })
+    # Row sums of squares of the orthogonalized rows: the last product's epilogue writes them as
+    # partials per 128 columns when the block is iterated as it lies (wide or square); a tall block
+    # is iterated transposed, and a foreign orthogonalizer knows nothing of this, so those take one
+    # sum per row from a pass of their own.
+    parts = _native.newton_schulz_rowsq_parts(cols) if native and k <= cols else 1
+    plan["rowsq"] = ((count * k, parts), torch.float32)
     if not selecting:
         plan["u"] = ((count, rows, cols), torch.float32)
     if native:
@@ -185,8 +194,10 @@ def open_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any], ar
 
 def run_front(ctx: RunContext) -> None:
     """Stages 1-2 and the pack: the HBM-bound front of a run (reads G, updates M, writes the operand)."""
+    global CURRENT_RUN
     bucket, group, buf = ctx.bucket, ctx.group, ctx.buf
     cols, k = bucket.cols, bucket.selected_rows
+    CURRENT_RUN = (ctx.count, bucket.rows, k, cols)
     decay = float(group[MOMENTUM_KEY])
     if ctx.selecting:
         with _stage("accumulate"):
@@ -211,24 +222,31 @@ def run_front(ctx: RunContext) -> None:
 
 def run_core(ctx: RunContext) -> RunResult:
     """Stages 3-4: the tensor-core part (Newton-Schulz) and the NorMuon scales."""
+    global CURRENT_RUN
     bucket, group, buf = ctx.bucket, ctx.group, ctx.buf
     rows, cols, k = bucket.rows, bucket.cols, bucket.selected_rows
+    CURRENT_RUN = (ctx.count, rows, k, cols)
     fn = bucket.orthogonalize
+    normalize = RowNormalization(group[ROW_NORMALIZATION_KEY]) is RowNormalization.NORMUON
+    parts = buf["rowsq"].shape[1]
+    fused = normalize and parts > 1
     if isinstance(fn, NativeOrthogonalizer):
         with _stage("newton_schulz"):
-            orthogonal = run_iteration(fn, buf["x"], k, cols, buf["ns"], buf.get("xt"))
+            orthogonal = run_iteration(fn, buf["x"], k, cols, buf["ns"], buf.get("xt"),
+                                       rowsq=buf["rowsq"] if fused else None)
     else:
         orthogonal = _foreign_orthogonalize(fn, ctx.source, ctx.index, float(group[MOMENTUM_KEY]), ctx.selecting,
                                             buf["x"])
-    normalize = RowNormalization(group[ROW_NORMALIZATION_KEY]) is RowNormalization.NORMUON
     with _stage("finish"):
-        if normalize:
+        if normalize and not fused:
             _native.row_sumsq_bf16(orthogonal, cols, buf["rowsq"])
         _native.normuon_rows(buf["rowsq"], ctx.variance, ctx.index, blocks=ctx.count, rows=rows, k=k, cols=cols,
                              weight=1.0 - float(group[MUON_BETA2_KEY]), eps=NORMALIZATION_EPS, step=ctx.step,
-                             normalize=normalize, denom=buf["denom"], scale=buf["scale"])
+                             normalize=normalize, denom=buf["denom"], scale=buf["scale"],
+                             parts=parts if fused else 1, step_device=bucket.step_device)
     return RunResult(params=ctx.params, rows_per_tensor=ctx.rows_per_tensor, count=ctx.count, rows=rows, k=k,
-                     cols=cols, orthogonal=orthogonal, rowmap=ctx.rowmap, denom=buf["denom"], scale=buf["scale"])
+                     cols=cols, orthogonal=orthogonal, rowmap=ctx.rowmap, denom=buf["denom"], scale=buf["scale"],
+                     decay_device=bucket.decay_device)
 
 
 def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
@@ -241,14 +259,45 @@ def prepare_run(bucket: Bucket, positions: Sequence[int], group: dict[str, Any],
 
 def apply_result(result: RunResult, group: dict[str, Any]) -> None:
     """Stage 5: decoupled weight decay on every row, the scaled update on the selected rows."""
-    params = result.params
-    # A channels-last weight is updated through a packed copy and written back.
-    targets = [p if p.is_contiguous() else p.detach().contiguous() for p in params]
+    apply_results([result], group)
+
+
+def apply_results(results: Sequence[RunResult], group: dict[str, Any], warps: int = 0) -> None:
+    """Stage 5 for several results of one bucket shape (the contributions of every rank to a round
+    of the sharded step) in ONE launch per 64 weights.  ``warps`` sets the CTA size (0: the default)."""
+    global CURRENT_RUN
+    first = results[0]
+    CURRENT_RUN = (sum(r.count for r in results), first.rows, first.k, first.cols)
     lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
+    params: list[Tensor] = []
+    targets: list[Tensor] = []
+    rows_per_tensor: list[int] = []
+    # device addresses of each tensor's first block within its result's buffers
+    o: list[int] = []
+    rowmap: list[int] = []
+    denom: list[int] = []
+    scale: list[int] = []
+    for result in results:
+        o_base, o_block = result.orthogonal.data_ptr(), result.k * result.orthogonal.stride(-2) * 2
+        map_base = None if result.rowmap is None else result.rowmap.data_ptr()
+        denom_base, scale_base = result.denom.data_ptr(), result.scale.data_ptr()
+        block = 0
+        for param, tensor_rows in zip(result.params, result.rows_per_tensor):
+            params.append(param)
+            # A channels-last weight is updated through a packed copy and written back.
+            targets.append(param if param.is_contiguous() else param.detach().contiguous())
+            rows_per_tensor.append(tensor_rows)
+            o.append(o_base + block * o_block)
+            if map_base is not None:
+                rowmap.append(map_base + block * result.rows * 4)
+            denom.append(denom_base + block * result.k * 4)
+            scale.append(scale_base + block * 4)
+            block += tensor_rows // result.rows
     with _stage("apply"):
-        _native.apply_run(targets, result.rows_per_tensor, result.orthogonal, result.rowmap, result.denom,
-                          result.scale, rows=result.rows, k=result.k, cols=result.cols,
-                          decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0)
+        _native.apply_round(targets, rows_per_tensor, o, rowmap or None, denom, scale,
+                            ldo=first.orthogonal.stride(-2), rows=first.rows, k=first.k, cols=first.cols,
+                            decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0,
+                            decay_device=first.decay_device, cta_warps=warps)
     for param, target in zip(params, targets):
         if target is not param:
             param.copy_(target)

@@ -40,6 +40,8 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_version": (c_char_p, ()),
     "dionw_device_status": (c_int, (POINTER(c_int),)),
     "dionw_launch_count": (c_int64, ()),
+    "dionw_check_device": (c_int, ()),
+    "dionw_selftest_wait_timeout": (c_int, (c_int64, c_void_p, c_void_p)),
     "dionw_accumulate_row_l1_run": (c_int, (_PP, c_int, _I64P, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p)),
     "dionw_accumulate_copy_decay_run": (
         c_int, (_PP, c_int, _I64P, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p)),
@@ -51,7 +53,8 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_transpose_2byte": (c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p)),
     "dionw_newton_schulz_workspace_bytes": (c_size_t, (c_int64, c_int64, c_int64, c_int)),
     "dionw_newton_schulz": (
-        c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p)),
+        c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p)),
+    "dionw_newton_schulz_rowsq_parts": (c_int64, (c_int64,)),
     "dionw_newton_schulz_static": (
         c_int, (c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p)),
     "dionw_symmetric_product": (
@@ -62,13 +65,18 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
                 c_int64, c_int64, c_int64, c_int, c_int, c_void_p)),
     "dionw_row_sumsq_bf16": (c_int, (c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p)),
     "dionw_normuon_rows": (
-        c_int, (c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_float, c_float, c_int,
-                c_void_p, c_void_p, c_void_p)),
+        c_int, (c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_float, c_float,
+                c_void_p, c_int, c_void_p, c_void_p, c_void_p)),
+    "dionw_apply_round": (
+        c_int, (_PP, _I64P, _PP, _PP, _PP, _PP, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int,
+                c_int, c_void_p)),
+    "dionw_write_scalars": (c_int, (c_void_p, POINTER(c_float), c_int64, c_void_p)),
     "dionw_apply_run": (
         c_int, (_PP, _I64P, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                 c_float, c_int, c_void_p)),
     "dionw_adamw_multi": (
-        c_int, (_PP, _PP, _PP, _PP, _PP, _I64P, c_int, c_float, c_float, c_float, c_float, c_float, c_void_p)),
+        c_int, (_PP, _PP, _PP, _PP, _PP, _I64P, c_int, c_float, c_float, c_float, c_float, c_float, c_void_p,
+                c_void_p)),
     "dionw_ema_multi": (c_int, (_PP, _PP, _I64P, c_int, c_int, c_float, c_int, c_void_p)),
     "dionw_ema_stage_pack": (c_int, (_PP, _I64P, _I64P, c_int, c_int, c_void_p, c_void_p)),
     "dionw_cpu_ema_job_start": (c_void_p, (_PP, _PP, _I64P, POINTER(c_uint8), c_int, c_float, c_void_p, c_int)),
@@ -149,6 +157,28 @@ def device_status() -> int:
     return value.value
 
 
+class DeviceWaitError(RuntimeError):
+    """A bounded wait inside a kernel ran out (``DIONW_ERR_DEVICE_WAIT``)."""
+
+
+def check_device() -> None:
+    """Synchronise the current device and raise if a kernel's bounded wait ran out since the last check.
+
+    Raises:
+        DeviceWaitError: The device status word was non-zero (it is cleared by the read).
+    """
+    status = library().dionw_check_device()
+    if status == -5:
+        raise DeviceWaitError(f"dionw_b200: {last_error()} (code {status})")
+    _check(status)
+
+
+def selftest_wait_timeout(limit_us: int, gave_up: Tensor) -> None:
+    """Launch the wait self-test on ``gave_up``'s device: a kernel that waits ``limit_us`` on a
+    barrier nothing arrives on, gives up and sets ``gave_up`` (int32 scalar) to 1."""
+    _check(library().dionw_selftest_wait_timeout(limit_us, gave_up.data_ptr(), _stream(gave_up)))
+
+
 # ---------------------------------------------------------------------------
 # momentum passes
 # ---------------------------------------------------------------------------
@@ -200,11 +230,18 @@ def newton_schulz_workspace_bytes(blocks: int, m: int, n: int, kind: int) -> int
     return int(library().dionw_newton_schulz_workspace_bytes(blocks, m, n, kind))
 
 
-def newton_schulz(x: Tensor, out: Tensor, m: int, n: int, kind: int, workspace: Tensor) -> None:
-    """``x``: ``[blocks, m, ldx]`` fp16/bf16 wide operand (overwritten); ``out`` bf16, may alias ``x``."""
+def newton_schulz_rowsq_parts(n: int) -> int:
+    """Partial sums per output row that ``newton_schulz`` writes into ``rowsq`` for ``n`` columns."""
+    return int(library().dionw_newton_schulz_rowsq_parts(n))
+
+
+def newton_schulz(x: Tensor, out: Tensor, m: int, n: int, kind: int, workspace: Tensor,
+                  rowsq: Tensor | None = None) -> None:
+    """``x``: ``[blocks, m, ldx]`` fp16/bf16 wide operand (overwritten); ``out`` bf16, may alias ``x``.
+    ``rowsq`` (fp32 ``[blocks * m, newton_schulz_rowsq_parts(n)]``): partial row sums of ``out**2``."""
     _check(library().dionw_newton_schulz(x.data_ptr(), out.data_ptr(), x.shape[0], m, n, x.stride(-2), kind,
                                          workspace.data_ptr(), workspace.numel() * workspace.element_size(),
-                                         _stream(x)))
+                                         _ptr(rowsq), _stream(x)))
 
 
 STATIC_SCRATCH_BYTES = 64 << 20
@@ -245,9 +282,12 @@ def row_sumsq_bf16(o: Tensor, cols: int, s: Tensor) -> None:
 
 
 def normuon_rows(s: Tensor, variance: Tensor, index: Tensor | None, *, blocks: int, rows: int, k: int, cols: int,
-                 weight: float, eps: float, step: float, normalize: bool, denom: Tensor, scale: Tensor) -> None:
-    _check(library().dionw_normuon_rows(s.data_ptr(), variance.data_ptr(), _ptr(index), blocks, rows, k, cols, weight,
-                                        eps, step, int(normalize), denom.data_ptr(), scale.data_ptr(), _stream(s)))
+                 weight: float, eps: float, step: float, normalize: bool, denom: Tensor, scale: Tensor,
+                 parts: int = 1, step_device: Tensor | None = None) -> None:
+    """``s`` holds ``parts`` partial sums per row; ``step_device`` (one fp32 on the device) overrides ``step``."""
+    _check(library().dionw_normuon_rows(s.data_ptr(), parts, variance.data_ptr(), _ptr(index), blocks, rows, k, cols,
+                                        weight, eps, step, _ptr(step_device), int(normalize), denom.data_ptr(),
+                                        scale.data_ptr(), _stream(s)))
 
 
 def apply_run(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Tensor, rowmap: Tensor | None,
@@ -258,18 +298,39 @@ def apply_run(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Tens
         denom.data_ptr(), scale.data_ptr(), rows, k, cols, decay_factor, int(has_decay), _stream(o)))
 
 
+def apply_round(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Sequence[int],
+                rowmap: Sequence[int] | None, denom: Sequence[int], scale: Sequence[int], *, ldo: int,
+                rows: int, k: int, cols: int, decay_factor: float, has_decay: bool,
+                decay_device: Tensor | None = None, cta_warps: int = 0) -> None:
+    """The weight update of tensors whose update rows lie in different buffers, in one launch:
+    ``o[i]``, ``rowmap[i]``, ``denom[i]``, ``scale[i]`` are the device addresses of the first block
+    of tensor ``i`` (bf16 rows, int32 row map, fp32 divisors, fp32 block scales)."""
+    n = len(weights)
+    _check(library().dionw_apply_round(
+        _ptr_array(weights), _i64_array(rows_per_tensor), (c_void_p * n)(*o),
+        None if rowmap is None else (c_void_p * n)(*rowmap), (c_void_p * n)(*denom), (c_void_p * n)(*scale), n, ldo,
+        rows, k, cols, decay_factor, _ptr(decay_device), int(has_decay), cta_warps, _stream(weights[0])))
+
+
+def write_scalars(dst: Tensor, values: Sequence[float]) -> None:
+    """``dst[:len(values)] = values`` (fp32, on the device), ordered on the current stream."""
+    n = len(values)
+    _check(library().dionw_write_scalars(dst.data_ptr(), (c_float * n)(*values), n, _stream(dst)))
+
+
 # ---------------------------------------------------------------------------
 # AdamW and EMA
 # ---------------------------------------------------------------------------
 def adamw_multi(params: Sequence[Tensor], grads: Sequence[Tensor], exp_avg: Sequence[Tensor],
                 exp_avg_sq: Sequence[Tensor], steps: Sequence[Tensor], *, lr: float, beta1: float, beta2: float,
-                weight_decay: float, eps: float) -> None:
+                weight_decay: float, eps: float, hyper_device: Tensor | None = None) -> None:
+    """``hyper_device`` (two fp32 on the device: lr, weight decay) overrides the two host values."""
     if not params:
         return
     _check(library().dionw_adamw_multi(
         _ptr_array(params), _ptr_array(grads), _ptr_array(exp_avg), _ptr_array(exp_avg_sq), _ptr_array(steps),
         _i64_array([p.numel() for p in params]), len(params), lr, beta1, beta2, weight_decay, eps,
-        _stream(params[0])))
+        _ptr(hyper_device), _stream(params[0])))
 
 
 def ema_multi(shadows: Sequence[Tensor], sources: Sequence[Tensor], *, weight: float, first: bool) -> None:

@@ -63,6 +63,20 @@ extern "C" int dionw_device_status(int* status) {
   return DIONW_OK;
 }
 
+extern "C" int dionw_check_device(void) {
+  int value = 0;
+  const int st = dionw_device_status(&value);
+  if (st != DIONW_OK) return st;
+  if (value != 0) {
+    dionw::set_error(
+        "a bounded wait inside a kernel ran out (device status 0x%x): the results of the work queued since the "
+        "last check are not to be trusted",
+        value);
+    return DIONW_ERR_DEVICE_WAIT;
+  }
+  return DIONW_OK;
+}
+
 // ---------------------------------------------------------------------------
 // CPU EMA worker
 // ---------------------------------------------------------------------------
@@ -183,15 +197,21 @@ void run_job(dionw_cpu_ema_job* job) {
         if (offset >= hi) break;
       }
     };
+    // The pool lives outside the try block: if a helper thread cannot be started, the ones
+    // already running are joined below instead of being destroyed while joinable (which would
+    // terminate the process), and the update is reported as failed.
+    std::vector<std::thread> pool;
+    int started = 1;
     try {
-      std::vector<std::thread> pool;
-      for (int w = 1; w < workers; ++w) pool.emplace_back(body, w);
-      body(0);
-      for (auto& t : pool) t.join();
+      pool.reserve(size_t(workers));
+      for (; started < workers; ++started) pool.emplace_back(body, started);
     } catch (const std::exception& e) {
       failure = DIONW_ERR_WORKER;
-      snprintf(job->failure_text, sizeof(job->failure_text), "CPU EMA worker failed: %s", e.what());
+      snprintf(job->failure_text, sizeof(job->failure_text), "CPU EMA worker could not start a helper thread: %s",
+               e.what());
     }
+    body(0);
+    for (auto& t : pool) t.join();
   }
   {
     std::lock_guard<std::mutex> lock(job->mutex);
@@ -230,7 +250,13 @@ extern "C" dionw_cpu_ema_job* dionw_cpu_ema_job_start(float* const* shadows, con
   job->weight = weight;
   job->event = static_cast<cudaEvent_t>(cuda_event);
   job->threads = threads;
-  job->worker = std::thread(run_job, job);
+  try {
+    job->worker = std::thread(run_job, job);
+  } catch (const std::exception& e) {   // thread creation failed: no exception crosses the C boundary
+    dionw::set_error("cpu_ema_job_start: the worker thread could not be started: %s", e.what());
+    delete job;
+    return nullptr;
+  }
   return job;
 }
 

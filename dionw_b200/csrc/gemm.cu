@@ -1,8 +1,8 @@
 // Host side of the tcgen05 GEMMs: tensor maps, launches, and the Newton-Schulz
 // product schedules built from them.
-#include <mutex>
-
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "gemm2_sm100.cuh"
 
@@ -59,6 +59,15 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int64_t inner, int64
   return DIONW_OK;
 }
 
+constexpr int kMaxDevices = 64;
+
+// Ordinal of the current device, clamped into the per-device tables.
+int current_device() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) device = 0;
+  return device;
+}
+
 // Products are launched with programmatic stream serialization (the kernels wait with
 // griddepcontrol.wait before they touch global memory), unless DIONW_GEMM_PDL=0.  Measured on the
 // Llama-3-8B-shaped step: 95.1-96.2 ms with it, 98.3-99.0 ms without (about 290 product launches per step).
@@ -73,10 +82,11 @@ bool use_dependent_launch() {
 template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Params& p, cudaStream_t stream) {
   auto kernel = gemm::gemm_kernel<InT, OutT, kBMajorMN, kSym>;
-  static bool configured = false;
-  if (!configured) {
+  static std::atomic<bool> configured[kMaxDevices];   // the attribute is per device
+  const int device = current_device();
+  if (!configured[device].load(std::memory_order_acquire)) {
     DIONW_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm::kSmemBytes)));
-    configured = true;
+    configured[device].store(true, std::memory_order_release);
   }
   const int total = p.tiles_per_batch * p.batches;
   if (total == 0) return DIONW_OK;
@@ -108,10 +118,11 @@ bool use_cta_pairs() {
 template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
 int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, cudaStream_t stream) {
   auto kernel = gemm2::gemm2_kernel<InT, OutT, kBMajorMN, kSym>;
-  static bool configured = false;
-  if (!configured) {
+  static std::atomic<bool> configured[kMaxDevices];   // the attribute is per device
+  const int device = current_device();
+  if (!configured[device].load(std::memory_order_acquire)) {
     DIONW_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm2::kSmemBytes)));
-    configured = true;
+    configured[device].store(true, std::memory_order_release);
   }
   // Pair tiles are 256 x 256.
   p.tiles_m = (p.m + gemm2::kPairM - 1) / gemm2::kPairM;
@@ -194,6 +205,7 @@ int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, i
   p.tiles_per_batch = host_sym_tiles(p.tiles_m);
   p.mirror_diagonal = same ? 0 : 1;
   p.status = device_status_word();
+  p.wait_ns = gemm::kWaitLimitNs;
   if (dtype == DIONW_F16) return launch_any<__half, __half, false, true>(map_a, map_b, p, stream);
   return launch_any<__nv_bfloat16, __nv_bfloat16, false, true>(map_a, map_b, p, stream);
 }
@@ -202,7 +214,7 @@ int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, i
 int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int64_t ldb, int64_t b_batch,
                  bool b_is_nk, const void* cin, int64_t ldc, int64_t cin_batch, float beta, void* out, int64_t ldo,
                  int64_t out_batch, int64_t blocks, int64_t m, int64_t n, int64_t kdim, int in_dtype, int out_dtype,
-                 cudaStream_t stream) {
+                 float* rowsq, cudaStream_t stream) {
   DIONW_REQUIRE(in_dtype == DIONW_F16 || in_dtype == DIONW_BF16, "batched_gemm: input dtype must be F16 or BF16");
   DIONW_REQUIRE(out_dtype == DIONW_F16 || out_dtype == DIONW_BF16, "batched_gemm: output dtype must be F16 or BF16");
   DIONW_REQUIRE(blocks > 0 && m > 0 && n > 0 && kdim > 0, "batched_gemm: empty problem");
@@ -234,7 +246,10 @@ int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int
   p.tiles_m = int((m + gemm::kBM - 1) / gemm::kBM);
   p.tiles_n = int((n + gemm::kBN - 1) / gemm::kBN);
   p.tiles_per_batch = p.tiles_m * p.tiles_n;
+  p.rowsq = rowsq;
+  p.rowsq_parts = 2 * p.tiles_n;   // both kernels' tiles are 256 columns wide
   p.status = device_status_word();
+  p.wait_ns = gemm::kWaitLimitNs;
   const bool f16 = in_dtype == DIONW_F16;
   const bool out_same = out_dtype == in_dtype;
   if (b_is_nk) {
@@ -265,5 +280,44 @@ extern "C" int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int
                                   int64_t m, int64_t n, int64_t kdim, int in_dtype, int out_dtype, void* stream) {
   const int64_t b_rows = b_is_nk ? n : kdim;
   return dionw::batched_gemm(a, lda, m * lda, b, ldb, b_rows * ldb, b_is_nk != 0, cin, ldc, m * ldc, beta, out, ldo,
-                             m * ldo, blocks, m, n, kdim, in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+                             m * ldo, blocks, m, n, kdim, in_dtype, out_dtype, nullptr,
+                             static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait.  One CTA of one warp initialises an mbarrier on
+// which nothing ever arrives (no TMA, no TMEM, no other CTA) and waits on it with
+// the products' own mbar_wait and a limit of `limit_ns`.  The wait runs out, the
+// kernel stores the wait code in the device status word and returns normally: the
+// context stays usable and the host reads the code with dionw_check_device().
+// ---------------------------------------------------------------------------
+namespace dionw {
+namespace {
+
+__global__ void __launch_bounds__(32)
+wait_selftest_kernel(int* status, uint64_t limit_ns, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    gemm::mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const bool ok = gemm::mbar_wait(&bar, 0u, &abort_flag, status, limit_ns);
+    if (gave_up != nullptr) *gave_up = ok ? 0 : 1;
+  }
+}
+
+}  // namespace
+}  // namespace dionw
+
+extern "C" int dionw_selftest_wait_timeout(int64_t limit_us, int* gave_up, void* stream) {
+  using namespace dionw;
+  DIONW_REQUIRE(limit_us > 0 && limit_us <= 100000, "selftest_wait_timeout: the limit must be 1 .. 100000 us (got %lld)",
+                (long long)limit_us);
+  wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_status_word(),
+                                                                        uint64_t(limit_us) * 1000ull, gave_up);
+  return launch_status("wait_selftest_kernel");
 }

@@ -212,7 +212,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
           uint8_t* a_dst = smem + size_t(s) * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           const uint32_t leader_full = peer_address(&full_bar[s], 0);
@@ -242,13 +242,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       for (int t = pair; t < total_tiles && ok; t += pairs, ++local) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * uint32_t(kBN);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
-          if (!mbar_wait(&full_bar[s], phase, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], phase, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + size_t(s) * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;

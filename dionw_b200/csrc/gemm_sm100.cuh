@@ -39,6 +39,7 @@ constexpr size_t kSmemBytes =
     size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kMirrorBytes;
 
 constexpr int kWaitCode = 0x7001;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // default limit of a bounded wait: two seconds
 
 struct Params {
   // epilogue operands (element pointers; strides in elements)
@@ -53,7 +54,10 @@ struct Params {
   int batches;
   int tiles_m, tiles_n, tiles_per_batch;
   int mirror_diagonal;   // symmetric schedule with B != A: also mirror inside the diagonal sub-blocks
-  int* status;
+  float* rowsq;          // nullable, general products only: [batches, m, rowsq_parts] partial row sums of out^2
+  int rowsq_parts;       // = 2 * tiles_n: one partial per 128 columns, written once each, summed by the reader
+  int* status;           // device status word (may be null: the code is then not recorded)
+  uint64_t wait_ns;      // limit of every bounded wait, in nanoseconds of %globaltimer
 };
 
 // ----------------------------------------------------------------------------
@@ -104,10 +108,10 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
-// Bounded wait: gives up after about two seconds, flags the failure and tells
-// the rest of the CTA to stop through `abort_flag`.
+// Bounded wait: gives up after `limit_ns` (two seconds unless the launch says otherwise), flags
+// the failure in the device status word and tells the rest of the CTA to stop through `abort_flag`.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+                                          int* status, uint64_t limit_ns = kWaitLimitNs) {
   uint32_t spins = 0;
   uint64_t start = 0;   // the timer is first read after 1024 failed tries: a wait that ends soon never pays for it
   while (!mbar_try(bar, parity)) {
@@ -115,9 +119,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag != 0) return false;
       const uint64_t now = global_ns();
       if (start == 0) start = now;
-      else if (now - start > 2000000000ull) {
+      else if (now - start > limit_ns) {
         *abort_flag = 1;
-        atomicExch(status, kWaitCode);
+        if (status != nullptr) atomicExch(status, kWaitCode);
         return false;
       }
     }
@@ -317,9 +321,14 @@ __device__ __forceinline__ bool epilogue_tile(const Params& p, int batch, int m_
     for (int it = 0; it < 4; ++it) ahead[it] = *reinterpret_cast<const uint4*>(base + size_t(8 * it) * p.ldc);
   };
   prefetch(first_chunk);   // does not depend on the accumulator: overlaps the wait below
-  if (!mbar_wait(acc_full_bar, acc_phase, abort_flag, p.status)) return false;
+  if (!mbar_wait(acc_full_bar, acc_phase, abort_flag, p.status, p.wait_ns)) return false;
   tc_fence_after();
   uint32_t* my_row = reinterpret_cast<uint32_t*>(stage + lane * kMirrorPitch);
+  // Sum of the squares of this row's rounded results over the warp's 128 columns, for NorMuon:
+  // the value is in registers here, so the row statistics need no second pass over the output.
+  // One partial per (row, 128 columns), added left to right: the order is fixed.
+  const bool want_sq = !kSym && p.rowsq != nullptr;
+  float sq = 0.0f;
 #pragma unroll 1
   for (int chunk = first_chunk; chunk < first_chunk + kBN / 64; ++chunk) {
     const int col0 = n_base + chunk * 32;
@@ -354,6 +363,13 @@ __device__ __forceinline__ bool epilogue_tile(const Params& p, int batch, int m_
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = from_float<OutT>(p.alpha * __uint_as_float(v[j]));
+      }
+      if (want_sq) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float f = to_float<OutT>(r[j]);
+          sq = fmaf(f, f, sq);
+        }
       }
       // result: row order -> staging tile
       const uint32_t* words = reinterpret_cast<const uint32_t*>(r);
@@ -408,6 +424,10 @@ __device__ __forceinline__ bool epilogue_tile(const Params& p, int batch, int m_
       float x = p.alpha * __uint_as_float(v[j]);
       if (cin_row != nullptr && col0 + j < p.n) x = fmaf(p.beta, to_float<InT>(cin_row[col0 + j]), x);
       r[j] = from_float<OutT>(x);
+      if (want_sq && col0 + j < p.n) {
+        const float f = to_float<OutT>(r[j]);
+        sq = fmaf(f, f, sq);
+      }
       if constexpr (kSym) r2[j] = (row == col0 + j) ? from_float<OutT>(to_float<OutT>(r[j]) + p.diag) : r[j];
     }
     OutT* dst = out_b + size_t(row) * p.ldo + col0;
@@ -437,6 +457,10 @@ __device__ __forceinline__ bool epilogue_tile(const Params& p, int batch, int m_
         }
       }
     }
+  }
+  if (want_sq && row_ok) {
+    const int part = 2 * (n_base / kBN) + first_chunk / (kBN / 64);
+    p.rowsq[(size_t(batch) * p.m + row) * p.rowsq_parts + part] = sq;
   }
   return true;
 }
@@ -494,7 +518,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
           uint8_t* a_dst = smem + size_t(s) * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
@@ -518,13 +542,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * uint32_t(kBN);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
-          if (!mbar_wait(&full_bar[s], phase, abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], phase, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + size_t(s) * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;

@@ -10,7 +10,7 @@ int symmetric_product(const void* a, const void* b, int64_t blocks, int64_t m, i
 int batched_gemm(const void* a, int64_t lda, int64_t a_batch, const void* b, int64_t ldb, int64_t b_batch,
                  bool b_is_nk, const void* cin, int64_t ldc, int64_t cin_batch, float beta, void* out, int64_t ldo,
                  int64_t out_batch, int64_t blocks, int64_t m, int64_t n, int64_t kdim, int in_dtype, int out_dtype,
-                 cudaStream_t stream);
+                 float* rowsq, cudaStream_t stream);
 
 namespace {
 
@@ -75,8 +75,10 @@ extern "C" size_t dionw_newton_schulz_workspace_bytes(int64_t blocks, int64_t m,
   return bytes_of(layout_of(blocks, m, n, round_up(n, 8), kind)) + 256;
 }
 
+extern "C" int64_t dionw_newton_schulz_rowsq_parts(int64_t n) { return n <= 0 ? 0 : 2 * ((n + 255) / 256); }
+
 extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m, int64_t n, int64_t ldx, int kind,
-                                   void* workspace, size_t workspace_bytes, void* stream_ptr) {
+                                   void* workspace, size_t workspace_bytes, float* rowsq, void* stream_ptr) {
   using namespace dionw;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   DIONW_REQUIRE(kind == DIONW_NS_GRAM || kind == DIONW_NS_POLAR_EXPRESS || kind == DIONW_NS_KELLER ||
@@ -129,7 +131,7 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
       if (i == kRestart) {
         // X <- Q X, G <- X X^T
         DIONW_STEP(batched_gemm(q, ldg, gb, xcur, ldx, xb, false, nullptr, 0, 0, 0.0f, x1, ldx, xb, blocks, m, n, m,
-                                dt, dt, stream));
+                                dt, dt, nullptr, stream));
         xcur = x1;
         DIONW_STEP(symmetric_product(xcur, nullptr, blocks, m, n, ldx, xb, 0, 0, nullptr, 0, 0, 1.0f, 0.0f, g, ldg, gb,
                                      nullptr, 0.0f, dt, stream));
@@ -147,7 +149,7 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
                                        gb, nullptr, 0.0f, dt, stream));
         else
           DIONW_STEP(batched_gemm(q, ldg, gb, z, ldg, gb, true, q, ldg, gb, float(k.a), qnext, ldg, gb, blocks, m,
-                                  m, m, dt, dt, stream));
+                                  m, m, dt, dt, nullptr, stream));
         void* t = q;
         q = qnext;
         qnext = t;
@@ -161,15 +163,15 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
                                        gb, nullptr, 0.0f, dt, stream));
         } else {
           DIONW_STEP(batched_gemm(g, ldg, gb, z, ldg, gb, true, g, ldg, gb, float(k.a), rz, ldg, gb, blocks, m, m,
-                                  m, dt, dt, stream));
+                                  m, dt, dt, nullptr, stream));
           DIONW_STEP(batched_gemm(z, ldg, gb, rz, ldg, gb, false, rz, ldg, gb, float(k.a), g, ldg, gb, blocks, m,
-                                  m, m, dt, dt, stream));
+                                  m, m, dt, dt, nullptr, stream));
         }
       }
     }
     // out = Q X in bf16
     DIONW_STEP(batched_gemm(q, ldg, gb, xcur, ldx, xb, false, nullptr, 0, 0, 0.0f, out, ldx, xb, blocks, m, n, m, dt,
-                            DIONW_BF16, stream));
+                            DIONW_BF16, rowsq, stream));
     return DIONW_OK;
   }
 
@@ -188,7 +190,7 @@ extern "C" int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m
     DIONW_STEP(symmetric_product(g, nullptr, blocks, m, m, ldg, gb, 0, 0, g, ldg, gb, float(k.c), float(k.b), poly, ldg, gb,
                                  nullptr, 0.0f, dt, stream));
     DIONW_STEP(batched_gemm(poly, ldg, gb, cur, ldx, xb, false, cur, ldx, xb, float(k.a), next, ldx, xb, blocks, m,
-                            n, m, dt, i == 4 ? DIONW_BF16 : dt, stream));
+                            n, m, dt, i == 4 ? DIONW_BF16 : dt, i == 4 ? rowsq : nullptr, stream));
     cur = next;
   }
 #undef DIONW_STEP

@@ -68,5 +68,5 @@ extern "C" int dionw_newton_schulz_static(void* x, void* out, int64_t blocks, in
   // Nothing in the scratch has to start at zero: every product of the schedule
   // writes the whole of its output before a later product reads it, so what the
   // previous call left behind is never looked at.
-  return dionw_newton_schulz(x, out, blocks, m, n, ldx, kind, scratch, kStaticScratchBytes, stream);
+  return dionw_newton_schulz(x, out, blocks, m, n, ldx, kind, scratch, kStaticScratchBytes, nullptr, stream);
 }

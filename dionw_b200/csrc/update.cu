@@ -59,12 +59,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // One CTA per block: new row variances, row denominators, block scale.
 __global__ void __launch_bounds__(kReduceThreads)
-normuon_rows_kernel(const float* __restrict__ s, float* __restrict__ variance, const int32_t* __restrict__ index,
-                    int rows, int k, float inv_count_cols, float weight, float eps, float step, bool normalize,
+normuon_rows_kernel(const float* __restrict__ s, int parts, float* __restrict__ variance,
+                    const int32_t* __restrict__ index, int rows, int k, float inv_count_cols, float weight, float eps,
+                    float step_host, const float* __restrict__ step_device, bool normalize,
                     float* __restrict__ denom, float* __restrict__ scale) {
   __shared__ float scratch[kReduceThreads];
   const long long b = blockIdx.x;
   const int tid = threadIdx.x;
+  const float step = step_device != nullptr ? *step_device : step_host;
   if (!normalize) {
     for (int r = tid; r < k; r += kReduceThreads) denom[b * k + r] = 1.0f;
     if (tid == 0) scale[b] = step;
@@ -73,7 +75,18 @@ normuon_rows_kernel(const float* __restrict__ s, float* __restrict__ variance, c
   float n0 = 0.0f, n1 = 0.0f;
   for (int r = tid; r < k; r += kReduceThreads) {
     const long long slot = b * rows + (index ? index[b * k + r] : r);
-    const float sr = s[b * k + r];
+    // a row's sum of squares arrives whole (parts == 1) or as partials per 128 columns,
+    // added here left to right
+    const float* partial = s + (b * k + r) * parts;
+    float sr = 0.0f;
+    if ((parts & 3) == 0 && (reinterpret_cast<uintptr_t>(s) & 15u) == 0) {
+      for (int j = 0; j < parts; j += 4) {   // same order, four partials per load
+        const float4 q = __ldcs(reinterpret_cast<const float4*>(partial + j));
+        sr = (((sr + q.x) + q.y) + q.z) + q.w;
+      }
+    } else {
+      for (int j = 0; j < parts; ++j) sr += partial[j];
+    }
     const float mean = sr * inv_count_cols;
     const float old = variance[slot];
     // torch.lerp: start + weight * (end - start) for weight < 0.5, else the mirrored form.
@@ -95,71 +108,90 @@ normuon_rows_kernel(const float* __restrict__ s, float* __restrict__ variance, c
 // ---------------------------------------------------------------------------
 // weights: decay every row, add the update to the selected rows
 // ---------------------------------------------------------------------------
+// One launch updates up to kTable weight tensors.  Every tensor brings its own
+// update rows, row map, row divisors and block scales (pointers at ITS first
+// block), so tensors whose updates were computed by different ranks, and lie in
+// different receive slots, share a launch.
 constexpr int kTable = 64;
-struct WeightTable {
-  void* ptr[kTable];
-  long long row_end[kTable];
+struct ApplyEntry {
+  float* w;
+  const uint16_t* o;        // bf16 [blocks of this tensor, k, ldo]
+  const int32_t* rowmap;    // [blocks of this tensor, rows] or null: every row is updated
+  const float* denom;       // [blocks of this tensor, k]
+  const float* scale;       // [blocks of this tensor]
+  long long row_end;        // rows of this and the earlier tensors of the launch
+};
+struct ApplyTable {
+  ApplyEntry e[kTable];
   int n;
 };
 
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-apply_run_kernel(const WeightTable tab, long long first_row, long long total_rows, const uint16_t* __restrict__ o,
-                 long long ldo, const int32_t* __restrict__ rowmap, const float* __restrict__ denom,
-                 const float* __restrict__ scale, long long rows, long long k, long long cols, float decay_factor,
-                 bool has_decay, bool vec) {
+// The kernel only streams: what hides the memory latency is the number of rows in flight, so the
+// register count is held down (32-bit indices inside a row, the update's scale folded once per row).
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 6)
+apply_run_kernel(const ApplyTable tab, long long total_rows, int ldo, int rows, int k, int cols, float decay_host,
+                 const float* __restrict__ decay_device, bool has_decay, bool vec) {
   const int lane = threadIdx.x & 31;
-  const long long local = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (local >= total_rows) return;
-  const long long row = first_row + local;  // row within the run
-  const long long b = row / rows;
-  const long long in_block = row - b * rows;
-  const long long pos = rowmap ? (long long)rowmap[row] : in_block;
-  if (pos < 0 && !has_decay) return;
-  int lo = 0, hi = tab.n - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (local < tab.row_end[mid]) hi = mid; else lo = mid + 1;
-  }
-  const long long start = lo == 0 ? 0 : tab.row_end[lo - 1];
-  float* w = reinterpret_cast<float*>(tab.ptr[lo]) + (local - start) * cols;
-  if (pos < 0) {
-    if (vec) {
+  const int warps = blockDim.x >> 5;   // one row per warp; the launch chooses the CTA size
+  const long long stride = (long long)gridDim.x * warps;
+  for (long long local = (long long)blockIdx.x * warps + (threadIdx.x >> 5); local < total_rows; local += stride) {
+    int lo = 0, hi = tab.n - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (local < tab.e[mid].row_end) hi = mid; else lo = mid + 1;
+    }
+    const long long row = local - (lo == 0 ? 0 : tab.e[lo - 1].row_end);  // row within the tensor
+    const int b = int(row / rows);
+    const int32_t* rowmap = tab.e[lo].rowmap;
+    const int pos = rowmap ? rowmap[row] : int(row - (long long)b * rows);
+    if (pos < 0 && !has_decay) continue;
+    float* __restrict__ w = tab.e[lo].w + row * cols;
+    const float decay_factor = decay_device != nullptr ? __ldg(decay_device) : decay_host;
+    if (pos < 0) {
+      if (vec) {
+        float4* w4 = reinterpret_cast<float4*>(w);
+        const int n4 = cols >> 2;
 #pragma unroll 4
-      for (long long e = 4LL * lane; e < cols; e += 128) {
-        float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
-        v.x = __fmul_rn(v.x, decay_factor); v.y = __fmul_rn(v.y, decay_factor);
-        v.z = __fmul_rn(v.z, decay_factor); v.w = __fmul_rn(v.w, decay_factor);
-        __stcs(reinterpret_cast<float4*>(w + e), v);
+        for (int i = lane; i < n4; i += 32) {
+          float4 v = __ldcs(w4 + i);
+          v.x = __fmul_rn(v.x, decay_factor); v.y = __fmul_rn(v.y, decay_factor);
+          v.z = __fmul_rn(v.z, decay_factor); v.w = __fmul_rn(v.w, decay_factor);
+          __stcs(w4 + i, v);
+        }
+      } else {
+        for (int e = lane; e < cols; e += 32) w[e] = __fmul_rn(w[e], decay_factor);
+      }
+      continue;
+    }
+    const long long orow = (long long)b * k + pos;
+    const uint16_t* __restrict__ src = tab.e[lo].o + orow * ldo;
+    const float d = tab.e[lo].denom[orow];
+    const float sc = tab.e[lo].scale[b];
+    if (vec) {
+      float4* w4 = reinterpret_cast<float4*>(w);
+      const uint2* s2 = reinterpret_cast<const uint2*>(src);
+      const int n4 = cols >> 2;
+#pragma unroll 4
+      for (int i = lane; i < n4; i += 32) {
+        float4 v = __ldcs(w4 + i);
+        const uint2 raw = __ldcs(s2 + i);
+        float x[4] = {v.x, v.y, v.z, v.w};
+        const float ov[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                             __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (has_decay) x[j] = __fmul_rn(x[j], decay_factor);
+          x[j] = __fadd_rn(x[j], __fmul_rn(__fdiv_rn(ov[j], d), sc));
+        }
+        __stcs(w4 + i, make_float4(x[0], x[1], x[2], x[3]));
       }
     } else {
-      for (long long e = lane; e < cols; e += 32) w[e] = __fmul_rn(w[e], decay_factor);
-    }
-    return;
-  }
-  const uint16_t* src = o + (b * k + pos) * ldo;
-  const float d = denom[b * k + pos];
-  const float sc = scale[b];
-  if (vec) {
-#pragma unroll 4
-    for (long long e = 4LL * lane; e < cols; e += 128) {
-      float4 v = __ldcs(reinterpret_cast<const float4*>(w + e));
-      const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(src + e));
-      float x[4] = {v.x, v.y, v.z, v.w};
-      const float ov[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                           __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (has_decay) x[i] = __fmul_rn(x[i], decay_factor);
-        x[i] = __fadd_rn(x[i], __fmul_rn(__fdiv_rn(ov[i], d), sc));
+      for (int e = lane; e < cols; e += 32) {
+        float x = w[e];
+        if (has_decay) x = __fmul_rn(x, decay_factor);
+        const float ov = __uint_as_float(uint32_t(src[e]) << 16);
+        w[e] = __fadd_rn(x, __fmul_rn(__fdiv_rn(ov, d), sc));
       }
-      __stcs(reinterpret_cast<float4*>(w + e), make_float4(x[0], x[1], x[2], x[3]));
-    }
-  } else {
-    for (long long e = lane; e < cols; e += 32) {
-      float x = w[e];
-      if (has_decay) x = __fmul_rn(x, decay_factor);
-      const float ov = __uint_as_float(uint32_t(src[e]) << 16);
-      w[e] = __fadd_rn(x, __fmul_rn(__fdiv_rn(ov, d), sc));
     }
   }
 }
@@ -198,7 +230,11 @@ __device__ __forceinline__ void adamw_math(float& p, float g, float& m, float& v
 }
 
 __global__ void __launch_bounds__(kAdamThreads)
-adamw_multi_kernel(const AdamTable tab, float lr, float beta1, float beta2, float weight_decay, float eps) {
+adamw_multi_kernel(const AdamTable tab, float lr_host, float beta1, float beta2, float weight_decay_host, float eps,
+                   const float* __restrict__ hyper_device) {
+  // learning rate and weight decay come from device memory when the caller keeps them there
+  const float lr = hyper_device != nullptr ? hyper_device[0] : lr_host;
+  const float weight_decay = hyper_device != nullptr ? hyper_device[1] : weight_decay_host;
   int lo = 0, hi = tab.n - 1;
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
@@ -349,6 +385,31 @@ int chunked_tables(const int64_t* numels, int n_tensors, Fill&& fill, Launch&& l
 
 using namespace dionw;
 
+// Step scalars kept in device memory: the values travel as kernel arguments (copied when the
+// launch is made, so the host may change its own copy at once) and are stored by one small kernel.
+constexpr int kScalarsPerLaunch = 512;
+struct ScalarTable {
+  float v[kScalarsPerLaunch];
+};
+
+__global__ void write_scalars_kernel(const ScalarTable tab, float* __restrict__ dst, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = tab.v[i];
+}
+
+extern "C" int dionw_write_scalars(float* dst, const float* values, int64_t n, void* stream_ptr) {
+  DIONW_REQUIRE(dst != nullptr && values != nullptr && n >= 0, "write_scalars: null table");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  for (int64_t start = 0; start < n; start += kScalarsPerLaunch) {
+    ScalarTable tab;
+    const int count = int(n - start < kScalarsPerLaunch ? n - start : kScalarsPerLaunch);
+    for (int i = 0; i < count; ++i) tab.v[i] = values[start + i];
+    write_scalars_kernel<<<1, 128, 0, stream>>>(tab, dst + start, count);
+    const int st = launch_status("write_scalars_kernel");
+    if (st != DIONW_OK) return st;
+  }
+  return DIONW_OK;
+}
+
 extern "C" int dionw_row_sumsq_bf16(const void* o, int64_t blocks, int64_t k, int64_t cols, int64_t ldo, float* s,
                                     void* stream_ptr) {
   DIONW_REQUIRE(blocks > 0 && k > 0 && cols > 0 && ldo >= cols, "row_sumsq_bf16: bad shape");
@@ -360,50 +421,85 @@ extern "C" int dionw_row_sumsq_bf16(const void* o, int64_t blocks, int64_t k, in
   return launch_status("row_sumsq_bf16_kernel");
 }
 
-extern "C" int dionw_normuon_rows(const float* s, float* variance, const int32_t* index, int64_t blocks, int64_t rows,
-                                  int64_t k, int64_t cols, float weight, float eps, float step, int normalize,
-                                  float* denom, float* scale, void* stream_ptr) {
-  DIONW_REQUIRE(blocks > 0 && rows > 0 && k > 0 && k <= rows && cols > 0, "normuon_rows: bad shape");
+extern "C" int dionw_normuon_rows(const float* s, int64_t parts, float* variance, const int32_t* index, int64_t blocks,
+                                  int64_t rows, int64_t k, int64_t cols, float weight, float eps, float step,
+                                  const float* step_device, int normalize, float* denom, float* scale,
+                                  void* stream_ptr) {
+  DIONW_REQUIRE(blocks > 0 && rows > 0 && k > 0 && k <= rows && cols > 0 && parts >= 1 && parts <= 4096,
+                "normuon_rows: bad shape");
   normuon_rows_kernel<<<unsigned(blocks), kReduceThreads, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
-      s, variance, index, int(rows), int(k), 1.0f / float(cols), weight, eps, step, normalize != 0, denom, scale);
+      s, int(parts), variance, index, int(rows), int(k), 1.0f / float(cols), weight, eps, step, step_device,
+      normalize != 0, denom, scale);
   return launch_status("normuon_rows_kernel");
+}
+
+extern "C" int dionw_apply_round(void* const* weights, const int64_t* rows_per_tensor, const void* const* o,
+                                 const int32_t* const* rowmap, const float* const* denom, const float* const* scale,
+                                 int n_tensors, int64_t ldo, int64_t rows, int64_t k, int64_t cols,
+                                 float decay_factor, const float* decay_device, int has_decay, int cta_warps,
+                                 void* stream_ptr) {
+  DIONW_REQUIRE(n_tensors > 0 && rows > 0 && k > 0 && cols > 0, "apply_round: empty round");
+  DIONW_REQUIRE(rows < (1ll << 31) && cols < (1ll << 31) && ldo < (1ll << 31), "apply_round: a block dimension exceeds 2^31");
+  DIONW_REQUIRE(cta_warps >= 0 && cta_warps <= kWarpsPerBlock, "apply_round: cta_warps must be 0 (default) .. %d",
+                kWarpsPerBlock);
+  const int warps = cta_warps == 0 ? kWarpsPerBlock : cta_warps;
+  DIONW_REQUIRE(weights && rows_per_tensor && o && denom && scale, "apply_round: null table");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  bool vec = cols % 4 == 0 && ldo % 4 == 0;
+  for (int i = 0; i < n_tensors; ++i) vec = vec && aligned16(weights[i]) && (reinterpret_cast<uintptr_t>(o[i]) & 7u) == 0;
+  for (int start = 0; start < n_tensors; start += kTable) {
+    ApplyTable tab;
+    tab.n = (n_tensors - start < kTable) ? n_tensors - start : kTable;
+    long long acc = 0;
+    for (int i = 0; i < tab.n; ++i) {
+      const int t = start + i;
+      DIONW_REQUIRE(rows_per_tensor[t] >= 0 && rows_per_tensor[t] % rows == 0,
+                    "apply_round: tensor %d has %lld rows, not a multiple of the block's %lld", t,
+                    (long long)rows_per_tensor[t], (long long)rows);
+      acc += rows_per_tensor[t];
+      tab.e[i] = ApplyEntry{static_cast<float*>(weights[t]), static_cast<const uint16_t*>(o[t]),
+                            rowmap ? rowmap[t] : nullptr, denom[t], scale[t], acc};
+    }
+    if (acc > 0) {
+      long long grid = (acc + warps - 1) / warps;
+      if (grid > 0x7FFFFFFFll) grid = 0x7FFFFFFFll;   // the kernel walks the rows with a stride
+      apply_run_kernel<<<unsigned(grid), warps * 32, 0, stream>>>(tab, acc, int(ldo), int(rows), int(k), int(cols),
+                                                                  decay_factor, decay_device, has_decay != 0, vec);
+      const int st = launch_status("apply_run_kernel");
+      if (st != DIONW_OK) return st;
+    }
+  }
+  return DIONW_OK;
 }
 
 extern "C" int dionw_apply_run(void* const* weights, const int64_t* rows_per_tensor, int n_tensors, const void* o,
                                int64_t ldo, const int32_t* rowmap, const float* denom, const float* scale,
                                int64_t rows, int64_t k, int64_t cols, float decay_factor, int has_decay,
                                void* stream_ptr) {
-  DIONW_REQUIRE(n_tensors > 0 && rows > 0 && k > 0 && cols > 0, "apply_run: empty run");
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  bool vec = cols % 4 == 0 && ldo % 4 == 0 && aligned16(o);
-  for (int i = 0; i < n_tensors; ++i) vec = vec && aligned16(weights[i]);
-  long long done = 0;
-  for (int start = 0; start < n_tensors; start += kTable) {
-    WeightTable tab;
-    tab.n = (n_tensors - start < kTable) ? n_tensors - start : kTable;
-    long long acc = 0;
-    for (int i = 0; i < tab.n; ++i) {
-      tab.ptr[i] = weights[start + i];
-      acc += rows_per_tensor[start + i];
-      tab.row_end[i] = acc;
-    }
-    if (acc > 0) {
-      const unsigned grid = unsigned((acc + kWarpsPerBlock - 1) / kWarpsPerBlock);
-      apply_run_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(tab, done, acc, static_cast<const uint16_t*>(o), ldo,
-                                                                 rowmap, denom, scale, rows, k, cols, decay_factor,
-                                                                 has_decay != 0, vec);
-      const int st = launch_status("apply_run_kernel");
-      if (st != DIONW_OK) return st;
-    }
-    done += acc;
+  DIONW_REQUIRE(n_tensors > 0 && n_tensors <= 1024 && rows > 0 && k > 0 && cols > 0 && rows_per_tensor != nullptr,
+                "apply_run: empty run (or more than 1024 tensors)");
+  // The tensors of a run lie one after the other in the run's buffers.
+  const void* o_of[1024];
+  const int32_t* map_of[1024];
+  const float* denom_of[1024];
+  const float* scale_of[1024];
+  long long row = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    const long long block = row / rows;
+    o_of[i] = static_cast<const uint16_t*>(o) + block * k * ldo;
+    map_of[i] = rowmap ? rowmap + row : nullptr;
+    denom_of[i] = denom + block * k;
+    scale_of[i] = scale + block;
+    row += rows_per_tensor[i];
   }
-  return DIONW_OK;
+  return dionw_apply_round(weights, rows_per_tensor, o_of, rowmap ? map_of : nullptr, denom_of, scale_of, n_tensors,
+                           ldo, rows, k, cols, decay_factor, nullptr, has_decay, 0, stream_ptr);
 }
 
 extern "C" int dionw_adamw_multi(void* const* params, const void* const* grads, void* const* exp_avg,
                                  void* const* exp_avg_sq, void* const* steps, const int64_t* numels, int n_tensors,
                                  float lr, float beta1, float beta2, float weight_decay, float eps,
-                                 void* stream_ptr) {
+                                 const float* hyper_device, void* stream_ptr) {
   DIONW_REQUIRE(n_tensors >= 0, "adamw_multi: negative tensor count");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   return chunked_tables<AdamTable, kAdamTable, kAdamChunk>(
@@ -419,7 +515,8 @@ extern "C" int dionw_adamw_multi(void* const* params, const void* const* grads, 
         adamw_bump_steps_kernel<<<1, kAdamTable, 0, stream>>>(tab);
         int st = launch_status("adamw_bump_steps_kernel");
         if (st != DIONW_OK) return st;
-        adamw_multi_kernel<<<blocks, kAdamThreads, 0, stream>>>(tab, lr, beta1, beta2, weight_decay, eps);
+        adamw_multi_kernel<<<blocks, kAdamThreads, 0, stream>>>(tab, lr, beta1, beta2, weight_decay, eps,
+                                                                hyper_device);
         return launch_status("adamw_multi_kernel");
       });
 }

@@ -128,6 +128,7 @@ class _SharedBucket:
     blocks: list[int]           # blocks per parameter
     owners: list[int]           # owner rank per parameter
     local: Bucket | None = None  # this rank's slab (owned parameters only)
+    decay_device: Tensor | None = None  # 1 - lr * weight_decay of the group, in the device table of step scalars
 
 
 @dataclass
@@ -159,6 +160,7 @@ class _ShardedCore(_DionCore):
         self._world = dist.get_world_size(process_group)
         self._rank = dist.get_rank(process_group)
         self._shared: list[_SharedBucket] | None = None
+        self._round_streams: dict[torch.device, tuple[Any, Any]] = {}
         super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
                          weight_decay=weight_decay, eps=eps, matrix_update=matrix_update)
 
@@ -233,6 +235,11 @@ class _ShardedCore(_DionCore):
         self._ensure_shared()
         return self._buckets or []
 
+    def _scalar_slots(self) -> list[Any]:
+        # every rank applies every bucket's update, so the buckets owned elsewhere need their
+        # group's decay factor in the device table too
+        return list(self._ensure_buckets()) + list(self._ensure_shared())
+
     # ---- the step ------------------------------------------------------------
     @torch.no_grad()
     def step(self, closure: Callable[[], float] | None = None) -> float | None:
@@ -241,6 +248,7 @@ class _ShardedCore(_DionCore):
             with torch.enable_grad():
                 loss = closure()
         gathers: list[Any] = []
+        self._refresh_scalars()
         if self.adamw_first:
             gathers.extend(self._step_adamw())
             self._step_matrices(None)
@@ -270,14 +278,31 @@ class _ShardedCore(_DionCore):
     def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
         return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
 
-    # Update elements one round may hold per rank (the single-GPU cap bounds it from above),
-    # and whether the weight update of round t runs on a side stream next to the Newton-Schulz
-    # of round t+1.  Measured on 2 x B200 with the Llama-3-8B shapes: in line with full-size
-    # rounds 60.4 ms/step; in line with 2^26-element rounds 63.2; overlapped 64.8 (2^26) and
-    # 68.7 (2^25) -- the streaming update slows the tensor-core products it runs beside by more
-    # than it hides, so both stay off.
+    # Update elements one round may hold per rank (the single-GPU cap bounds it from above), and
+    # whether the weight update of round t runs beside the Newton-Schulz of round t+1.
+    #
+    # The update of a round is 8 B per weight element on EVERY rank (decoupled decay of all rows):
+    # it does not shrink with the number of GPUs and is the largest stage of the step on 8.  With
+    # ``overlap_apply`` the rounds' own work (accumulate ... Newton-Schulz, and the gathers) runs on
+    # a high-priority stream, the updates and AdamW on a default-priority one.  Two things make
+    # that pay, where a first version only moved the time around: the update is launched with
+    # CTAs of four warps (``apply_warps``), small enough in registers that two of them fit beside a
+    # resident tensor-core CTA, and the priority lets a product's CTAs take an SM before the
+    # update's queued CTAs do, so a product no longer waits for the update's grid to drain.
+    # ``round_elements`` cuts the costliest bucket into several rounds so that its own update has
+    # later Newton-Schulz work to hide behind.  Same kernels, same inputs: the results are
+    # bit-identical to the in-line order.
     round_elements = 1 << 28
     overlap_apply = False
+    apply_warps = 4
+
+    def _streams(self, device: torch.device) -> tuple[Any, Any]:
+        """(high-priority stream for the rounds, default-priority stream for the updates)."""
+        pair = self._round_streams.get(device)
+        if pair is None:
+            pair = self._round_streams[device] = (torch.cuda.Stream(device=device, priority=-1),
+                                                  torch.cuda.Stream(device=device))
+        return pair
 
     def _step_matrices(self, after_first_round: Callable[[], None] | None) -> None:
         """Every round of the matrix step; ``after_first_round`` is called once the first round's
@@ -291,84 +316,89 @@ class _ShardedCore(_DionCore):
             return
         device = shared[0].params[0].device
         main = torch.cuda.current_stream(device)
-        side = self._side_streams.get(device)
-        if side is None:
-            side = self._side_streams[device] = torch.cuda.Stream(device=device)
-        if not self.overlap_apply:
-            side = main
-        else:
+        if self.overlap_apply:
+            compute, side = self._streams(device)
+            compute.wait_stream(main)
             side.wait_stream(main)
+        else:
+            compute = side = main
         pending: _Round | None = None
         applied: list[Any] = []  # applied[t]: event recorded on the side stream after round t's update
         round_id = 0
-        for sb in shared:
-            group = self.param_groups[sb.group_index]
-            selecting = sb.k < sb.rows
-            per_rank = [[i for i, o in enumerate(sb.owners) if o == r] for r in range(world)]
-            runs = []
-            for members in per_rank:
-                sizes = [None if sb.params[i].grad is None else sb.blocks[i] * sb.k * sb.cols for i in members]
-                runs.append([[members[j] for j in run] for run in split_runs(sizes, limit)])
-            for t in range(max((len(r) for r in runs), default=0)):
-                chosen = [r[t] if t < len(r) else [] for r in runs]
-                counts = [sum(sb.blocks[i] for i in c) for c in chosen]
-                slot = max(_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, selecting))[1]
-                           if c else 0 for c in counts)
-                if round_id >= 2:
-                    # This round reuses the send and receive arenas of round_id - 2.
-                    main.wait_event(applied[round_id - 2])
-                name = f"run{round_id % 2}"
-                _workspace.arena(device, slot, name)
-                if chosen[me]:
-                    local_index = {id(p): j for j, p in enumerate(sb.local.params)}
-                    positions = [local_index[id(sb.params[i])] for i in chosen[me]]
-                    _matrix_step.prepare_run(sb.local, positions, group, arena=name)
-                send = _workspace.arena(device, slot, name)[:slot]
-                if world == 1:
-                    recv, work = send, None
-                else:
-                    recv = _workspace.arena(device, slot * world, f"recv{round_id % 2}")[: slot * world]
-                    work = self._all_gather(recv, send)
-                issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
-                                [[sb.blocks[i] for i in c] for c in chosen], sb, group)
-                if round_id == 0 and after_first_round is not None:
-                    after_first_round()
-                if pending is not None:
-                    applied.append(self._apply_round(pending, main, side))
-                pending = issued
-                round_id += 1
-        if pending is not None:
-            applied.append(self._apply_round(pending, main, side))
-        if side is not main:
+        with torch.cuda.stream(compute):
+            for sb in shared:
+                group = self.param_groups[sb.group_index]
+                selecting = sb.k < sb.rows
+                per_rank = [[i for i, o in enumerate(sb.owners) if o == r] for r in range(world)]
+                runs = []
+                for members in per_rank:
+                    sizes = [None if sb.params[i].grad is None else sb.blocks[i] * sb.k * sb.cols for i in members]
+                    runs.append([[members[j] for j in run] for run in split_runs(sizes, limit)])
+                for t in range(max((len(r) for r in runs), default=0)):
+                    chosen = [r[t] if t < len(r) else [] for r in runs]
+                    counts = [sum(sb.blocks[i] for i in c) for c in chosen]
+                    slot = max(_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, selecting))[1]
+                               if c else 0 for c in counts)
+                    if round_id >= 2:
+                        # This round reuses the send and receive arenas of round_id - 2.
+                        compute.wait_event(applied[round_id - 2])
+                    name = f"run{round_id % 2}"
+                    _workspace.arena(device, slot, name)
+                    if chosen[me]:
+                        local_index = {id(p): j for j, p in enumerate(sb.local.params)}
+                        positions = [local_index[id(sb.params[i])] for i in chosen[me]]
+                        _matrix_step.prepare_run(sb.local, positions, group, arena=name)
+                    send = _workspace.arena(device, slot, name)[:slot]
+                    if world == 1:
+                        recv, work = send, None
+                    else:
+                        recv = _workspace.arena(device, slot * world, f"recv{round_id % 2}")[: slot * world]
+                        work = self._all_gather(recv, send)
+                    issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
+                                    [[sb.blocks[i] for i in c] for c in chosen], sb, group)
+                    if round_id == 0 and after_first_round is not None:
+                        with torch.cuda.stream(side):
+                            after_first_round()
+                    if pending is not None:
+                        applied.append(self._apply_round(pending, compute, side))
+                    pending = issued
+                    round_id += 1
+            if pending is not None:
+                applied.append(self._apply_round(pending, compute, side))
+        if compute is not main:
+            main.wait_stream(compute)
             main.wait_stream(side)
 
-    def _apply_round(self, rnd: _Round, main: Any, side: Any) -> Any:
-        """Every rank's contribution of one round applied to this replica, on the side stream."""
+    def _apply_round(self, rnd: _Round, compute: Any, side: Any) -> Any:
+        """Every rank's contribution of one round applied to this replica with one launch, on the side stream."""
         with torch.cuda.stream(side):
             if rnd.work is not None:
-                rnd.work.wait()          # the side stream waits for the gather
-            elif side is not main:
-                side.wait_stream(main)   # one rank: the "received" data is the local result
+                rnd.work.wait()             # the side stream waits for the gather
+            elif side is not compute:
+                side.wait_stream(compute)   # one rank: the "received" data is the local result
             sb = rnd.bucket
             selecting = sb.k < sb.rows
+            results = []
             for rank, count in enumerate(rnd.counts):
                 if count == 0:
                     continue
                 got = _workspace.views(rnd.recv,
                                        _matrix_step.exchange_plan(count, sb.rows, sb.k, sb.cols, selecting),
                                        base=rank * rnd.slot)
-                result = _matrix_step.RunResult(
+                results.append(_matrix_step.RunResult(
                     params=rnd.params[rank], rows_per_tensor=[b * sb.rows for b in rnd.blocks[rank]], count=count,
                     rows=sb.rows, k=sb.k, cols=sb.cols, orthogonal=got["x"], rowmap=got.get("rowmap"),
-                    denom=got["denom"], scale=got["scale"])
-                _matrix_step.apply_result(result, rnd.group)
+                    denom=got["denom"], scale=got["scale"], decay_device=sb.decay_device))
+            if results:
+                _matrix_step.apply_results(results, rnd.group,
+                                           warps=self.apply_warps if side is not compute else 0)
             done = torch.cuda.Event()
             done.record(side)
         return done
 
     def _step_adamw(self) -> list[Any]:
         gathers: list[Any] = []
-        for group in self.param_groups:
+        for index, group in enumerate(self.param_groups):
             if RouteKind(group[ROUTE_KEY]) is not RouteKind.ADAMW:
                 continue
             lists: tuple[list[Tensor], ...] = ([], [], [], [], [])
@@ -397,7 +427,8 @@ class _ShardedCore(_DionCore):
             beta1, beta2 = group["betas"]
             with _matrix_step._stage("adamw"):
                 _native.adamw_multi(*lists, lr=float(group["lr"]), beta1=float(beta1), beta2=float(beta2),
-                                    weight_decay=float(group["weight_decay"]), eps=float(group["eps"]))
+                                    weight_decay=float(group["weight_decay"]), eps=float(group["eps"]),
+                                    hyper_device=self._adamw_hyper(index, lists[0][0].device))
             gathers.extend(self._all_gather(whole, piece) for whole, piece in rebuilt)
         return gathers
 
@@ -524,6 +555,7 @@ class ShardedDion(IntegratedEMAOptimizer, _ShardedCore):
         70B-shaped slice alone is 68 GB).  Every rank saves its own; ``load_sharded_state_dict``
         takes it back on the same rank of a group of the same size with the same parameters.
         """
+        self.check_device()
         helper = self._ema_helper
         if helper is not None:
             helper.flush_pending_updates()

@@ -84,9 +84,36 @@ class IntegratedEMAOptimizer(Optimizer):
             helper.finalize_updates()
         return loss
 
+    # ---- device status -------------------------------------------------------
+    def check_device(self) -> None:
+        """Synchronise the parameters' devices and raise if a kernel of an earlier step gave up a wait.
+
+        The tensor-core kernels bound every wait on a barrier; one that runs out stores a
+        code in a device status word and returns instead of hanging.  ``step()`` never
+        synchronises, so the word is read where the optimizer synchronises anyway:
+        ``state_dict()`` and ``swap_ema_weights()`` call this first, and a training loop may
+        call it as often as it likes.  Fail fast, never swallow
+        (src/dionw/ema/_cpu_job.py:108-137 is the reference's form of the same rule).
+
+        Raises:
+            dionw_b200._native.DeviceWaitError: The weights and state written since the last
+                check are not to be trusted.
+        """
+        from dionw_b200 import _native
+
+        devices = {p.device for group in self.param_groups for p in group["params"] if p.is_cuda}
+        for device in sorted(devices, key=lambda d: d.index or 0):
+            with torch.cuda.device(device):
+                _native.check_device()
+
     # ---- saving and loading ------------------------------------------------
     def state_dict(self) -> dict[str, Any]:
-        """The optimizer state plus the shadows and ``_ema_step_count`` (pending work finished first)."""
+        """The optimizer state plus the shadows and ``_ema_step_count`` (pending work finished first).
+
+        Raises:
+            dionw_b200._native.DeviceWaitError: See ``check_device``.
+        """
+        self.check_device()
         helper = self._ema_helper
         if helper is None:
             return super().state_dict()
@@ -172,6 +199,7 @@ class IntegratedEMAOptimizer(Optimizer):
             return False
         if self._stored_params:
             raise RuntimeError("EMA weights are already swapped in")
+        self.check_device()
         helper.flush_pending_updates()
         context = type(self).__name__
         params = self._iter_trainable_params()

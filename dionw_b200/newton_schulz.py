@@ -75,18 +75,22 @@ class NativeOrthogonalizer:
 
 
 def run_iteration(fn: NativeOrthogonalizer, x: Tensor, rows: int, cols: int, scratch: Tensor,
-                  xt: Tensor | None) -> Tensor:
+                  xt: Tensor | None, rowsq: Tensor | None = None) -> Tensor:
     """Iterate on ``x`` ``[N, rows, ld]`` (normalised, in ``fn.dtype``); returns bf16 ``[N, rows, ld]``.
 
     Wide and square blocks are iterated in place.  Tall ones go through ``xt``, a
     ``[N, cols, padded(rows)]`` buffer of the same dtype.  ``scratch`` holds
-    ``fn.workspace_bytes(...)`` bytes.
+    ``fn.workspace_bytes(...)`` bytes.  ``rowsq`` (wide and square blocks only):
+    fp32 ``[N * rows, newton_schulz_rowsq_parts(cols)]``, filled with partial row
+    sums of the squared result by the last product's epilogue.
     """
     m, n = min(rows, cols), max(rows, cols)
     out = x if x.dtype is torch.bfloat16 else x.view(torch.bfloat16)
     if rows <= cols:
-        _native.newton_schulz(x, out, m, n, fn.code, scratch)
+        _native.newton_schulz(x, out, m, n, fn.code, scratch, rowsq)
         return out
+    if rowsq is not None:
+        raise ValueError("row sums come with wide and square blocks only: a tall block is iterated transposed")
     if xt is None:
         raise ValueError("tall blocks need the transposed buffer")
     _native.transpose_2byte(x[..., :cols], xt)

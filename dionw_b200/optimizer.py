@@ -30,7 +30,7 @@ from dionw_b200._keys import (
     NUM_HEADS_KEY, ROUTE_KEY, ROW_NORMALIZATION_KEY, STRUCTURAL_KEYS,
 )
 from dionw_b200._matrix_step import (
-    MAX_RUN_ELEMENTS, apply_result, open_run, run_core, run_elements, run_front, step_run,
+    MAX_RUN_ELEMENTS, apply_result, open_run, run_core, run_elements, run_front, step_run, step_size,
 )
 from dionw_b200.ema import EMAConfig, IntegratedEMAOptimizer, ProfileRegion, no_profile
 from dionw_b200.matrix_update import DION3_UPDATE, MatrixUpdate, MomentumForm, RowNormalization
@@ -148,6 +148,9 @@ class _DionCore(Optimizer):
         self._graph: tuple[tuple[Any, ...], torch.cuda.CUDAGraph] | None = None
         self._graph_warm: tuple[Any, ...] | None = None
         self._graph_recordings = 0
+        self._scalar_tables: dict[torch.device, Tensor] = {}
+        self._scalar_layout: tuple[Any, ...] | None = None
+        self._scalar_values: list[float] | None = None
         self.graph_kernels = 0   # kernel launches held by the current recording
         self.graph_replays = 0   # steps executed by replaying a recording
         super().__init__(params, defaults)
@@ -224,6 +227,7 @@ class _DionCore(Optimizer):
                 loss = closure()
         runs = [(bucket, run) for bucket in self._ensure_buckets() for run in self._runs_of(bucket)]
         devices = {bucket.momentum.device for bucket, _ in runs}
+        self._refresh_scalars()
         if self.graph_replay and self._graph_eligible(runs):
             self._step_replayed(runs)
         elif self.overlap_streams and len(runs) > 1 and len(devices) == 1 and step_run is _sequential_step_run:
@@ -234,8 +238,57 @@ class _DionCore(Optimizer):
 
     def _step_in_sequence(self, runs: list[tuple[Bucket, list[int]]]) -> None:
         for bucket, run in runs:
-            step_run(bucket, run, self.param_groups[bucket.group_index], self.state)
+            # the library looks up per-device facts (SM count, status word) for the current device
+            with torch.cuda.device(bucket.momentum.device):
+                step_run(bucket, run, self.param_groups[bucket.group_index], self.state)
         self._step_adamw_groups()
+
+    # The scalars of a step that follow the learning rate -- ``-step_size`` per bucket,
+    # ``1 - lr * weight_decay`` per group, AdamW's lr and weight decay -- live in a small fp32 table
+    # on each device, as the reference keeps ``-step_size`` in a 0-d device tensor
+    # (src/dionw/_buckets.py:57-58, _matrix_step.py:115, _row_normalization.py:48-49): kernels read
+    # them from there, so a scheduled learning rate changes no launch and a recorded step stays
+    # valid.  Layout: four slots per group (lr, weight decay, decay factor, unused), then one per
+    # bucket.  The table is rewritten, by one small launch ordered before the step's kernels,
+    # only when a value differs from what was written last.
+    def _scalar_slots(self) -> list[Any]:
+        """What owns a per-bucket slot, in slot order (a sharded optimizer adds to it)."""
+        return list(self._ensure_buckets())
+
+    def _refresh_scalars(self) -> None:
+        from dionw_b200 import _native
+
+        owners = self._scalar_slots()
+        groups = self.param_groups
+        values: list[float] = []
+        for group in groups:
+            lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
+            values += [lr, weight_decay, 1.0 - lr * weight_decay, 0.0]
+        base = len(values)
+        for owner in owners:
+            values.append(-step_size(owner, float(groups[owner.group_index]["lr"])) if isinstance(owner, Bucket) else 0.0)
+        devices = sorted({p.device for group in groups for p in group["params"] if p.is_cuda},
+                         key=lambda d: d.index or 0)
+        layout = (len(groups), tuple(id(o) for o in owners), tuple(devices))
+        if layout != self._scalar_layout:
+            self._scalar_tables = {d: torch.zeros(len(values), dtype=torch.float32, device=d) for d in devices}
+            self._scalar_layout, self._scalar_values = layout, None
+            for slot, owner in enumerate(owners):
+                table = self._scalar_tables[owner.params[0].device]
+                at = 4 * owner.group_index + 2
+                owner.decay_device = table[at:at + 1]
+                if isinstance(owner, Bucket):
+                    owner.step_device = table[base + slot:base + slot + 1]
+        if values != self._scalar_values:
+            for device, table in self._scalar_tables.items():
+                with torch.cuda.device(device):
+                    _native.write_scalars(table, values)
+            self._scalar_values = values
+
+    def _adamw_hyper(self, group_index: int, device: torch.device) -> Tensor | None:
+        """``{lr, weight_decay}`` of a group in the device table."""
+        table = self._scalar_tables.get(device)
+        return None if table is None else table[4 * group_index:4 * group_index + 2]
 
     # Optional replay of the step from a CUDA graph.  The reference measures 7-17 ms of host
     # dispatch per step of its own (README.md:514-516 and bench/host_dispatch.py:28-56 there); here a step
@@ -279,9 +332,12 @@ class _DionCore(Optimizer):
         """Everything a recorded step bakes in (see ``graph_replay``)."""
         from dionw_b200 import _workspace
 
-        parts: list[Any] = [_workspace.generation, torch.cuda.current_device()]
+        parts: list[Any] = [_workspace.generation, torch.cuda.current_device(),
+                            tuple(t.data_ptr() for t in self._scalar_tables.values())]
         for group in self.param_groups:
-            parts.append((float(group["lr"]), float(group["weight_decay"]), float(group[MOMENTUM_KEY]),
+            # lr and the weight decay's value are read from the device table; only whether there is
+            # a decay at all selects code
+            parts.append((float(group["weight_decay"]) > 0.0, float(group[MOMENTUM_KEY]),
                           float(group[MUON_BETA2_KEY]), tuple(map(float, group["betas"])), float(group["eps"])))
             adamw = RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW
             for p in group["params"]:
@@ -330,9 +386,9 @@ class _DionCore(Optimizer):
         self._graph_recordings += 1
 
     def _step_adamw_groups(self) -> None:
-        for group in self.param_groups:
+        for index, group in enumerate(self.param_groups):
             if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
-                adamw_step(group, self.state)
+                adamw_step(group, self.state, hyper=lambda device, index=index: self._adamw_hyper(index, device))
 
     # Optional two-stream step: the tensor-core part of run i (Newton-Schulz, on the
     # caller's stream) overlaps the HBM-bound parts of its neighbours on a side

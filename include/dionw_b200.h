@@ -55,6 +55,18 @@ int64_t dionw_launch_count(void);
 /* Reads and clears the device status word (non-zero: a bounded wait inside a
  * kernel ran out).  Synchronises the device; meant for tests and diagnostics. */
 int dionw_device_status(int* status);
+/* Synchronises the device, reads and clears the status word, and returns
+ * DIONW_ERR_DEVICE_WAIT (with the code in the error text) when a bounded wait
+ * ran out since the last check, DIONW_OK otherwise.  The reference fails fast and
+ * never swallows an error (src/dionw/ema/_cpu_job.py:108-137); this is the call
+ * the host makes wherever it synchronises anyway (checkpoints, weight swaps). */
+int dionw_check_device(void);
+/* Self-test of the bounded wait: one small kernel waits `limit_us` microseconds
+ * (1 .. 100000) on a barrier nothing arrives on, gives up, stores the wait code
+ * in the status word and returns normally; *gave_up (device int, may be NULL) is
+ * set to 1.  dionw_check_device() afterwards returns DIONW_ERR_DEVICE_WAIT once.
+ * No counterpart in the reference. */
+int dionw_selftest_wait_timeout(int64_t limit_us, int* gave_up, void* stream);
 
 /* ---- momentum passes ---------------------------------------------------- */
 
@@ -122,9 +134,16 @@ size_t dionw_newton_schulz_workspace_bytes(int64_t blocks, int64_t m, int64_t n,
  * src/dionw/_symmetric_kernels.py:252-312) computed on one triangle of tiles
  * by tcgen05 tensor-core kernels fed by TMA.  POLAR_EXPRESS / KELLER follow
  * quintic_triton (src/dionw/_polar_express.py:74-104, src/dionw/_keller.py). */
+/* rowsq (nullable, fp32 [blocks * m, dionw_newton_schulz_rowsq_parts(n)]): the
+ * epilogue of the last product also writes, per output row, the sum of the
+ * squares of its bf16 results over each 128 columns -- what normalize_rows
+ * (src/dionw/_row_normalization.py:41-60) reduces the output to -- so NorMuon
+ * needs no second pass over the output (dionw_normuon_rows adds the parts). */
 int dionw_newton_schulz(void* x, void* out, int64_t blocks, int64_t m, int64_t n,
                         int64_t ldx, int kind, void* workspace, size_t workspace_bytes,
-                        void* stream);
+                        float* rowsq, void* stream);
+/* Partial sums per output row that dionw_newton_schulz writes into rowsq. */
+int64_t dionw_newton_schulz_rowsq_parts(int64_t n);
 
 /* The same iteration for callers that have no scratch to give: a host bound to
  * this ABI without torch's allocator, a serving loop whose memory was budgeted at
@@ -170,7 +189,9 @@ int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, i
 
 /* ---- NorMuon and the weight update -------------------------------------- */
 
-/* s[b*k + r] = sum_c o[b, r, c]^2 for a bf16 batch [blocks, k, ldo]. */
+/* s[b*k + r] = sum_c o[b, r, c]^2 for a bf16 batch [blocks, k, ldo] (used where
+ * dionw_newton_schulz cannot hand the row sums over: tall blocks, which are
+ * iterated transposed, and foreign orthogonalizers). */
 int dionw_row_sumsq_bf16(const void* o, int64_t blocks, int64_t k, int64_t cols,
                          int64_t ldo, float* s, void* stream);
 
@@ -179,11 +200,17 @@ int dionw_row_sumsq_bf16(const void* o, int64_t blocks, int64_t k, int64_t cols,
  * back to variance[b, index[b, r]] (index NULL: row r); denom = sqrt(v) + eps;
  * scale[b] = ||O|| / max(||O/denom||, eps) * step.  normalize = 0 gives
  * denom = 1, scale = step and leaves variance alone
- * (RowNormalization.NONE, src/dionw/_row_normalization.py:35-36). */
-int dionw_normuon_rows(const float* s, float* variance, const int32_t* index,
+ * (RowNormalization.NONE, src/dionw/_row_normalization.py:35-36).
+ * s is [blocks * k, parts]: a row's sum of squares is the sum of its parts,
+ * taken left to right (parts = 1: dionw_row_sumsq_bf16's output).
+ * step_device (nullable) overrides step with a value read from device memory,
+ * as the reference keeps -step_size in a 0-d device tensor so that a scheduled
+ * learning rate costs nothing (src/dionw/_buckets.py:57-58,
+ * src/dionw/_row_normalization.py:48-49). */
+int dionw_normuon_rows(const float* s, int64_t parts, float* variance, const int32_t* index,
                        int64_t blocks, int64_t rows, int64_t k, int64_t cols,
-                       float weight, float eps, float step, int normalize,
-                       float* denom, float* scale, void* stream);
+                       float weight, float eps, float step, const float* step_device,
+                       int normalize, float* denom, float* scale, void* stream);
 
 /* W <- W * decay_factor on every row (when has_decay), then
  * W[row] += (float(o[b, p, :]) / denom[b, p]) * scale[b] for each selected row
@@ -194,6 +221,28 @@ int dionw_apply_run(void* const* weights, const int64_t* rows_per_tensor, int n_
                     const float* scale, int64_t rows, int64_t k, int64_t cols,
                     float decay_factor, int has_decay, void* stream);
 
+/* The same update for tensors whose update rows do not lie in one buffer (a
+ * round of the sharded step applies the contributions of every rank with one
+ * launch): o[i], rowmap[i] (array or entries nullable), denom[i], scale[i] point
+ * at the first block of tensor i.  decay_device (nullable) overrides
+ * decay_factor with a value read from device memory (the reference's decay is
+ * `1 - lr * wd` of the current lr, src/dionw/_matrix_step.py:280).  cta_warps
+ * (0 = the default 8, else 1..8) sets the CTA size, one row per warp: CTAs of
+ * four warps are small enough in registers to run beside a resident tensor-core
+ * CTA, for a launch that overlaps the Newton-Schulz of the next round. */
+int dionw_apply_round(void* const* weights, const int64_t* rows_per_tensor,
+                      const void* const* o, const int32_t* const* rowmap,
+                      const float* const* denom, const float* const* scale, int n_tensors,
+                      int64_t ldo, int64_t rows, int64_t k, int64_t cols, float decay_factor,
+                      const float* decay_device, int has_decay, int cta_warps, void* stream);
+
+/* dst[0..n) <- values[0..n) (host array), stream-ordered: the values are copied
+ * into the launch, so the host array may be reused at once.  The step's scalars
+ * (-step_size per bucket, 1 - lr*wd per group, lr and wd per AdamW group) live
+ * in device memory so that a recorded step can be replayed under a learning-rate
+ * schedule (src/dionw/_buckets.py:57-58 keeps them in 0-d device tensors). */
+int dionw_write_scalars(float* dst, const float* values, int64_t n, void* stream);
+
 /* ---- AdamW and EMA ------------------------------------------------------ */
 
 /* Adds one to every fp32 step counter, then one fused decoupled-decay AdamW
@@ -202,7 +251,8 @@ int dionw_apply_run(void* const* weights, const int64_t* rows_per_tensor, int n_
 int dionw_adamw_multi(void* const* params, const void* const* grads, void* const* exp_avg,
                       void* const* exp_avg_sq, void* const* steps, const int64_t* numels,
                       int n_tensors, float lr, float beta1, float beta2, float weight_decay,
-                      float eps, void* stream);
+                      float eps, const float* hyper_device, void* stream);
+/* hyper_device (nullable): {lr, weight_decay} read from device memory instead. */
 
 /* shadow <- source (first = 1) or shadow += weight * (source - shadow) for
  * every tensor (weight = 1 - decay < 0.5 form of torch.lerp; else

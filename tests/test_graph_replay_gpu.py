@@ -65,14 +65,53 @@ def test_replayed_step_is_bit_identical(monkeypatch) -> None:
     _same_state(opt_a, opt_b)
 
 
-def test_a_changed_learning_rate_is_recorded_anew() -> None:
+def test_a_scheduled_learning_rate_keeps_the_recording(monkeypatch) -> None:
+    """The step scalars that follow the learning rate (-step_size, 1 - lr * wd, AdamW's lr and weight
+    decay) are read from a device table, as the reference keeps -step_size in a 0-d device tensor
+    (src/dionw/_buckets.py:57-58): twenty steps of a cosine schedule (lr and weight decay both
+    moving) replay ONE recording and equal, bit for bit, the same steps run as launches -- with the
+    scalars read from the device table and with them passed as kernel arguments."""
+    import math
+
+    (net_a, opt_a), (net_b, opt_b), (net_c, opt_c) = (_build(True, ema=False), _build(False, ema=False),
+                                                      _build(False, ema=False))
+    monkeypatch.setattr(opt_c, "_refresh_scalars", lambda: None)   # host scalars: the kernels' other source
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    for step in range(20):
+        lr = 3e-4 * 0.5 * (1.0 + math.cos(math.pi * step / 20))
+        for opt in (opt_a, opt_b, opt_c):
+            for group in opt.param_groups:
+                group["lr"] = lr
+                if group["weight_decay"] > 0.0:
+                    group["weight_decay"] = 0.05 * (1.0 - 0.02 * step)
+        for pa, pb, pc in zip(net_a.parameters(), net_b.parameters(), net_c.parameters()):
+            g = torch.randn(pa.shape, device=DEV, generator=gen) * 1e-3
+            pa.grad.copy_(g)
+            pb.grad.copy_(g)
+            pc.grad.copy_(g)
+        opt_a.step()
+        opt_b.step()
+        opt_c.step()
+        torch.cuda.synchronize()
+        for pa, pb, pc in zip(net_a.parameters(), net_b.parameters(), net_c.parameters()):
+            assert torch.equal(pa, pb), step
+            assert torch.equal(pb, pc), step
+    assert opt_a._graph_recordings == 1 and opt_a.graph_replays == 19
+    assert all(b.step_device is None for b in opt_c._buckets)
+    _same_state(opt_a, opt_b)
+    _same_state(opt_b, opt_c)
+
+
+def test_a_weight_decay_switched_off_is_recorded_anew() -> None:
+    """Whether a group decays at all selects code in the weight update, so that IS part of a
+    recording's key: switching it off costs one step as launches and one new recording."""
     (net_a, opt_a), (net_b, opt_b) = _build(True, ema=False), _build(False, ema=False)
     gen = torch.Generator(device=DEV).manual_seed(2)
     for step in range(7):
         if step == 3:
             for opt in (opt_a, opt_b):
                 for group in opt.param_groups:
-                    group["lr"] = 1e-4
+                    group["weight_decay"] = 0.0
         _fill_grads(net_a, net_b, gen)
         opt_a.step()
         opt_b.step()

@@ -531,3 +531,150 @@ def test_cpu_ema_job_updates_pinned_shadows(native) -> None:
     job.close()
     for s, e in zip(shadows, expect):
         torch.testing.assert_close(s, e, rtol=0, atol=1e-7)
+
+
+# ---------------------------------------------------------------------------
+# row statistics from the last product's epilogue, one launch per round, device scalars, bounded waits
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("kind,blocks,m,n", [(0, 2, 256, 4096), (0, 1, 1024, 1280), (0, 3, 200, 520), (0, 2, 512, 512),
+                                             (1, 2, 384, 1000), (2, 1, 640, 640)])
+def test_last_product_also_writes_the_row_sums_of_squares(native, kind, blocks, m, n) -> None:
+    """``rowsq`` handed to the iteration comes back as partial sums per 128 columns whose total is the
+    row's sum of squares of the bf16 output (what ``row_sumsq_bf16`` computes in a pass of its own),
+    for the Gram schedule, the standard iteration and odd shapes; the output itself is unchanged."""
+    x32 = torch.randn(blocks, m, n, generator=_gen(21))
+    ld = (n + 7) // 8 * 8
+    dtype = torch.float16 if kind == 0 else torch.bfloat16
+    xn = (x32 / (torch.linalg.vector_norm(x32, dim=(-2, -1), keepdim=True) + 1e-8)).to(dtype)
+    outs = []
+    parts = native.newton_schulz_rowsq_parts(n)
+    assert parts == 2 * ((n + 255) // 256)
+    rowsq = torch.full((blocks * m, parts), float("nan"), device=DEV)
+    for with_rowsq in (False, True):
+        x = torch.zeros(blocks, m, ld, dtype=dtype, device=DEV)
+        x[..., :n] = xn.to(DEV)
+        ws = torch.empty(native.newton_schulz_workspace_bytes(blocks, m, n, kind), dtype=torch.uint8, device=DEV)
+        out = torch.zeros(blocks, m, ld, dtype=torch.bfloat16, device=DEV)
+        native.newton_schulz(x, out, m, n, kind, ws, rowsq if with_rowsq else None)
+        outs.append(out)
+    assert native.device_status() == 0
+    assert torch.equal(outs[0], outs[1])
+    assert not torch.isnan(rowsq).any()
+    separate = torch.empty(blocks * m, device=DEV)
+    native.row_sumsq_bf16(outs[1], n, separate)
+    torch.testing.assert_close(rowsq.sum(dim=1), separate, rtol=2e-6, atol=0)
+    exact = outs[1][..., :n].double().square().sum(-1).view(-1)
+    torch.testing.assert_close(rowsq.double().sum(dim=1), exact, rtol=2e-6, atol=0)
+    # NorMuon from the parts and from the whole sums: the same divisors and scales
+    variance = torch.rand(blocks, m, generator=_gen(22)).to(DEV) * 1e-3
+    results = []
+    for s, p in ((rowsq, parts), (separate, 1)):
+        v = variance.clone()
+        denom, scale = torch.empty(blocks * m, device=DEV), torch.empty(blocks, device=DEV)
+        native.normuon_rows(s, v, None, blocks=blocks, rows=m, k=m, cols=n, weight=0.05, eps=1e-8, step=-0.01,
+                            normalize=True, denom=denom, scale=scale, parts=p)
+        results.append((v, denom, scale))
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b, rtol=2e-6, atol=0)
+
+
+def test_one_launch_applies_the_results_of_several_runs(native) -> None:
+    """``apply_round`` over tensors whose update rows lie in three different buffers (what the ranks
+    of a sharded round send) equals ``apply_run`` once per buffer, bit for bit -- with the decay
+    factor passed as an argument, read from device memory, and with CTAs of four warps."""
+    g = _gen(30)
+    rows, cols, k = 96, 520, 24
+    ld = (cols + 7) // 8 * 8
+    factor = 1.0 - 3e-4 * 0.05
+    runs = []
+    for blocks_per_tensor in ([1, 2], [3], [1, 1, 1]):
+        count = sum(blocks_per_tensor)
+        o = torch.zeros(count, k, ld, dtype=torch.bfloat16)
+        o[..., :cols] = torch.randn(count, k, cols, generator=g).bfloat16() * 0.05
+        index = oracle.select_rows(torch.rand(count, rows, generator=g), k)
+        rowmap = torch.full((count, rows), -1, dtype=torch.int32)
+        rowmap.scatter_(1, index, torch.arange(k, dtype=torch.int32).expand(count, k))
+        runs.append({"weights": [torch.randn(b * rows, cols, generator=g) * 0.02 for b in blocks_per_tensor],
+                     "blocks": blocks_per_tensor, "o": o.to(DEV), "rowmap": rowmap.to(DEV),
+                     "denom": (torch.rand(count * k, generator=g) + 0.5).to(DEV),
+                     "scale": (torch.rand(count, generator=g) * -0.01).to(DEV)})
+    expect = []
+    for run in runs:
+        w = [t.to(DEV) for t in run["weights"]]
+        native.apply_run(w, [b * rows for b in run["blocks"]], run["o"], run["rowmap"], run["denom"], run["scale"],
+                         rows=rows, k=k, cols=cols, decay_factor=factor, has_decay=True)
+        expect += w
+    device_factor = torch.tensor([factor], dtype=torch.float32, device=DEV)
+    for decay_device, warps in ((None, 0), (device_factor, 0), (device_factor, 4)):
+        weights, per_tensor, o, rowmap, denom, scale = [], [], [], [], [], []
+        for run in runs:
+            block = 0
+            for t, b in zip(run["weights"], run["blocks"]):
+                weights.append(t.to(DEV))
+                per_tensor.append(b * rows)
+                o.append(run["o"][block].data_ptr())
+                rowmap.append(run["rowmap"][block].data_ptr())
+                denom.append(run["denom"][block * k:].data_ptr())
+                scale.append(run["scale"][block:].data_ptr())
+                block += b
+        native.apply_round(weights, per_tensor, o, rowmap, denom, scale, ldo=ld, rows=rows, k=k, cols=cols,
+                           decay_factor=123.0 if decay_device is not None else factor, has_decay=True,
+                           decay_device=decay_device, cta_warps=warps)
+        for got, want in zip(weights, expect):
+            assert torch.equal(got, want)
+
+
+def test_adamw_and_normuon_read_their_scalars_from_device_memory(native) -> None:
+    """lr and weight decay of AdamW, and the step of NorMuon, taken from device memory give the bits
+    of the same values passed as arguments; ``write_scalars`` is ordered on the stream."""
+    g = _gen(31)
+    table = torch.zeros(600, device=DEV)
+    values = [float(v) for v in torch.rand(600, generator=g)]
+    native.write_scalars(table, values)
+    assert torch.equal(table.cpu(), torch.tensor(values, dtype=torch.float32))
+    native.write_scalars(table, [3e-4, 0.05, -0.0123])
+    n = 5000
+    start = [torch.randn(n, generator=g) * 0.02 for _ in range(4)]
+    outs = []
+    for hyper in (None, table[:2]):
+        p, grad, m, v = (t.to(DEV).clone() for t in start)
+        v = v.abs()
+        steps = torch.zeros((), device=DEV)
+        for _ in range(2):
+            native.adamw_multi([p], [grad], [m], [v], [steps], lr=3e-4 if hyper is None else 9.0, beta1=0.9,
+                               beta2=0.95, weight_decay=0.05 if hyper is None else 9.0, eps=1e-8, hyper_device=hyper)
+        outs.append((p, m, v))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    s = torch.rand(2 * 40, generator=g).to(DEV)
+    scales = []
+    for step_device in (None, table[2:3]):
+        variance = torch.zeros(2, 40, device=DEV)
+        denom, scale = torch.empty(80, device=DEV), torch.empty(2, device=DEV)
+        native.normuon_rows(s, variance, None, blocks=2, rows=40, k=40, cols=64, weight=0.05, eps=1e-8,
+                            step=-0.0123 if step_device is None else 5.0, normalize=True, denom=denom, scale=scale,
+                            step_device=step_device)
+        scales.append(scale)
+    assert torch.equal(scales[0], scales[1])
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(native) -> None:
+    """The tensor-core kernels bound every wait on a barrier.  The library's self-test kernel waits
+    one millisecond on a barrier nothing arrives on, with the products' own wait routine: it must
+    RETURN, leave the wait code in the device status word, ``check_device`` must raise once, and an
+    ordinary product right after must be correct."""
+    assert native.device_status() == 0
+    gave_up = torch.zeros((), dtype=torch.int32, device=DEV)
+    native.selftest_wait_timeout(1000, gave_up)
+    torch.cuda.synchronize()
+    assert int(gave_up) == 1
+    with pytest.raises(native.DeviceWaitError, match="0x7001"):
+        native.check_device()
+    native.check_device()   # the word was cleared by the read
+    a = (torch.randn(2, 300, 520, generator=_gen(5)) / 520**0.5).half().to(DEV)
+    out = torch.empty(2, 300, 304, dtype=torch.float16, device=DEV)
+    native.symmetric_product(a, out)
+    torch.cuda.synchronize()
+    expect = a.float() @ a.float().mT
+    assert rel_l2(out[..., :300], expect) < 2e-3
+    assert native.device_status() == 0
