@@ -315,16 +315,79 @@ def measured_peaks() -> tuple[dict, str]:
 # ---------------------------------------------------------------------------
 # the CPU arm (oracle) — also the cpu_baseline of the GPU arm
 # ---------------------------------------------------------------------------
+_REFERENCE_CPU: tuple[object | None, str] | None = None
+
+
+def reference_on_cpu() -> tuple[object | None, str]:
+    """The UNMODIFIED reference package from ``baseline/_ref`` (git-ignored; it travels with the
+    repository's working copy), made to step on CPU tensors: its Triton launches are replaced by the
+    torch forms the reference itself uses for non-contiguous gradients
+    (src/dionw/_matrix_step.py:190-192, :240-251) and by ``bmm``/``baddbmm`` for the two symmetric
+    products, ``torch.compile`` wrappers are taken off with ``inspect.unwrap`` (as its own
+    bench/static_vs_dynamic.py:40-41 does) and the CUDA-only parameter check is switched off.  The
+    optimizer, bucket packing, Newton-Schulz schedule, NorMuon, AdamW call and EMA stay its own code.
+    Returns ``(module, "")`` or ``(None, why)``."""
+    global _REFERENCE_CPU
+    if _REFERENCE_CPU is not None:
+        return _REFERENCE_CPU
+    import inspect
+
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "dionw" / "__init__.py").exists():
+        _REFERENCE_CPU = (None, "no reference package under baseline/_ref")
+        return _REFERENCE_CPU
+    sys.path.insert(0, str(ref_root))
+    try:
+        import dionw as ref
+        import dionw._buckets as buckets
+        import dionw._gram as gram
+        import dionw._matrix_step as matrix_step
+        import dionw._polar_express as polar
+        import dionw._row_normalization as row_norm
+        import dionw.optimizer as ref_optimizer
+
+        ref_optimizer._check_param = lambda param: None
+        gram.ns_line_1 = lambda a: a @ a.mT
+        gram.ns_line_2 = lambda a, alpha, beta: torch.baddbmm(a, a, a.mT, beta=beta, alpha=alpha)
+        polar.ns_line_1 = lambda a, *, out=None: torch.matmul(a, a.mT, out=out)
+        polar.ns_line_2 = lambda a, alpha, beta, *, out=None: (torch.baddbmm if a.ndim == 3 else torch.addmm)(
+            a, a, a.mT, beta=beta, alpha=alpha, out=out)
+
+        def row_l1(grad, momentum, scores, cols):
+            momentum.add_(grad.view(momentum.shape))
+            scores.copy_(torch.linalg.vector_norm(momentum.view(-1, cols), ord=1, dim=-1))
+
+        def copy_decay(grad, momentum, out, decay, *, nesterov):
+            momentum.add_(grad.view(momentum.shape))
+            if nesterov:
+                momentum.mul_(decay)
+                out.copy_((momentum + grad.view(momentum.shape)).view(out.shape))
+            else:
+                out.copy_(momentum.view(out.shape))
+                momentum.mul_(decay)
+
+        matrix_step.accumulate_row_l1, matrix_step.accumulate_copy_decay = row_l1, copy_decay
+        row_norm.normalize_rows = inspect.unwrap(row_norm.normalize_rows)
+        plain = {kind: inspect.unwrap(ref.newton_schulz.newton_schulz_fn(kind)) for kind in ref.NewtonSchulz}
+        buckets.newton_schulz_fn = lambda kind: plain[kind]
+        _REFERENCE_CPU = (ref, "")
+    except Exception as exc:  # noqa: BLE001 - the reason is reported in the JSON line
+        _REFERENCE_CPU = (None, f"the reference does not import on this host: {exc!r}")
+    finally:
+        sys.path.remove(str(ref_root))
+    return _REFERENCE_CPU
+
+
 def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
-    """Times the CPU oracle on a bounded sample of the workload and scales it to the whole set.
+    """Times the reference's step on the host cores, on a bounded sample of the workload scaled to
+    the whole set.  The reference itself (``reference_on_cpu``, ``kind: "reference"``) when its
+    package is there, else the oracle port (``kind: "port"``).
 
     Matrix part: one whole layer's blocks, multiplied by the layer count, where a layer is
     affordable (d_model <= 4096: about 3 s per sample step on 16 threads at the Llama-3-8B shapes);
     for wider models the attention blocks alone, scaled by Newton-Schulz FLOPs.  AdamW part: a
-    slice of the embedding table (at most 2^24 elements) plus one norm vector, scaled by elements.
-    The single-matrix configuration is run whole."""
-    from oracle import dion_oracle as oracle
-
+    slice of the embedding table (at most 2^24 elements), scaled by elements.  The single-matrix
+    configuration is run whole."""
     layers, d, dkv, dff, vocab = CONFIGS[config]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -360,29 +423,59 @@ def cpu_sample_step(config: str, steps: int, warmup: int) -> dict:
                 times.append((time.perf_counter() - t0) * 1e3)
         return statistics.median(times)
 
-    weights = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
-    grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
-    matrices = oracle.OracleDion(matrix=[(w, 0.25 if min(w.shape) >= 1024 else 1.0) for w in weights],
-                                 adamw=[], lr=LR, weight_decay=WEIGHT_DECAY)
-    matrix_ms = median_ms(lambda: matrices.step(grads, []))
+    adam_sample = min(adam_total, 1 << 24)
+    reference, why_not = reference_on_cpu()
+    if reference is not None:
+        kind = "reference"
+        who = "the reference package itself (torch eager on CPU tensors, its Triton launches replaced by its own torch forms)"
+
+        class Sample(nn.Module):
+            def __init__(self, sizes) -> None:
+                super().__init__()
+                self.mats = nn.ParameterList([nn.Parameter(torch.randn(size, generator=gen) * 0.02) for size in sizes])
+
+        def stepper(module: nn.Module, routes=None):
+            groups, _ = reference.param_groups(module, routes=routes)
+            optimizer = reference.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY)
+            for p in module.parameters():
+                p.grad = torch.randn(p.shape, generator=gen) * 1e-3
+            return optimizer.step
+
+        matrix_step = stepper(Sample(shapes))
+        table = nn.Embedding(1, adam_sample)   # an embedding goes to AdamW, with weight decay, like the model's tables
+        with torch.no_grad():
+            table.weight.normal_(0.0, 0.02, generator=gen)
+        adam_step = stepper(table)
+    else:
+        from oracle import dion_oracle as oracle
+
+        kind = "port"
+        who = f"CPU oracle port ({why_not})"
+        weights = [torch.randn(size, generator=gen) * 0.02 for size in shapes]
+        grads = [torch.randn(size, generator=gen) * 1e-3 for size in shapes]
+        matrices = oracle.OracleDion(matrix=[(w, 0.25 if min(w.shape) >= 1024 else 1.0) for w in weights],
+                                     adamw=[], lr=LR, weight_decay=WEIGHT_DECAY)
+        matrix_step = lambda: matrices.step(grads, [])  # noqa: E731
+        table = torch.randn(adam_sample, generator=gen) * 0.02
+        table_grad = torch.randn(adam_sample, generator=gen) * 1e-3
+        vectors = oracle.OracleDion(matrix=[], adamw=[(table, None)], lr=LR, weight_decay=WEIGHT_DECAY)
+        adam_step = lambda: vectors.step([], [table_grad])  # noqa: E731
+
+    matrix_ms = median_ms(matrix_step)
     sample_flops = sum(block_flops(r, c) for r, c in shapes)
     model_flops = layers * sum(block_flops(r, c) for r, c in per_layer)
     matrix_scale = model_flops / sample_flops
-
-    adam_sample = min(adam_total, 1 << 24)
-    table = torch.randn(adam_sample, generator=gen) * 0.02
-    table_grad = torch.randn(adam_sample, generator=gen) * 1e-3
-    vectors = oracle.OracleDion(matrix=[], adamw=[(table, None)], lr=LR, weight_decay=WEIGHT_DECAY)
-    adam_ms = median_ms(lambda: vectors.step([], [table_grad]))
+    adam_ms = median_ms(adam_step)
     adam_scale = adam_total / adam_sample
-
     scaled = matrix_ms * matrix_scale + adam_ms * adam_scale
+    whole = matrix_scale == 1.0 and adam_scale == 1.0
     return {
-        "value": scaled, "unit": "ms", "cores": cores, "kind": "port",
-        "sample": (f"CPU oracle (torch eager, {cores} threads), median of {steps} steps after {warmup}: "
+        "value": scaled, "unit": "ms", "cores": cores, "kind": kind,
+        "sample": (f"{who}, {cores} threads, median of {steps} steps after {warmup}: "
                    f"{what}: {matrix_ms:.1f} ms x{matrix_scale:.0f} (Newton-Schulz FLOPs of the whole set / of the "
                    f"sample); AdamW on {adam_sample} elements: {adam_ms:.2f} ms x{adam_scale:.1f} (elements)"),
-        "sample_ms": matrix_ms + adam_ms,
+        "sample_ms": matrix_ms + adam_ms, "extrapolated": not whole,
+        "scale": {"matrix": matrix_scale, "adamw": adam_scale},
     }
 
 
@@ -398,7 +491,8 @@ def run_reference_arm(args) -> None:
         "dtype": "fp32 state, fp16 Newton-Schulz", "data": "synthetic",
         "config": {"workload": f"{args.config}-shaped parameter set, fp32 masters, Dion3 fraction 0.25 + AdamW",
                    "lr": LR, "weight_decay": WEIGHT_DECAY,
-                   "arm": "reference's algorithm on host CPU cores (oracle port)"},
+                   "arm": ("the reference package on host CPU cores" if base["kind"] == "reference"
+                           else "reference's algorithm on host CPU cores (oracle port)")},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -591,8 +685,11 @@ def run_ns_microbench(args) -> None:
         y = whole()[0].float()
         err = float(torch.linalg.matrix_norm(y @ y.T - torch.eye(m, device=device)))
         flops = NS_BATCH * flops_newton_schulz(m, n)
+        executed = NS_BATCH * flops_newton_schulz_executed(m, n)
         rows_out.append({"shape": [m, n], "batch": NS_BATCH, "call_ms": whole_ms, "iteration_ms": iter_ms,
                          "TFLOP/s": flops / iter_ms / 1e9, "frac_of_burst_peak": flops / iter_ms / 1e9 / peaks["bf16_tflops"],
+                         "executed_TFLOP/s": executed / iter_ms / 1e9,
+                         "executed_frac_of_burst_peak": executed / iter_ms / 1e9 / peaks["bf16_tflops"],
                          "orthogonality_error": err, "error_per_sqrt_m": err / m**0.5})
         del x, packed, scratch, work, y
         torch.cuda.empty_cache()
@@ -675,6 +772,23 @@ def run_gemm_sustained(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_sub_bench(flags: list[str], timeout: float) -> dict:
+    """Another arm of this file in a process of its own (it needs the GPU to itself); its JSON line."""
+    try:
+        done = subprocess.run([sys.executable, str(ROOT / "bench.py"), *flags], capture_output=True, text=True,
+                              timeout=timeout, cwd=str(ROOT))
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"bench.py {' '.join(flags)} did not finish within {timeout:.0f} s"}
+    for line in reversed(done.stdout.splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except json.JSONDecodeError:
+                break
+    return {"unavailable": f"bench.py {' '.join(flags)} printed no JSON line (exit code {done.returncode}): "
+                           f"{done.stderr[-300:]}"}
+
+
 # ---------------------------------------------------------------------------
 # correctness of the sharded step, checked inside the distributed run (outside the timed region)
 # ---------------------------------------------------------------------------
@@ -746,7 +860,7 @@ def sharded_parity(device, rank: int, dist) -> dict:
 # ---------------------------------------------------------------------------
 def run_gpu_arm(args) -> None:
     import dionw_b200 as dionw
-    from dionw_b200 import _adamw, _matrix_step, _native
+    from dionw_b200 import _matrix_step, _native
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -763,6 +877,15 @@ def run_gpu_arm(args) -> None:
                 os.environ.setdefault(key, value)
         dist.init_process_group("nccl", device_id=device)
     _native.library()
+    # The reference's own GPU step on the same workload (its Triton + cuBLAS path), measured first, in a
+    # process of its own, while this one holds no device memory: the denominator of "times faster than
+    # the reference's step on one B200".
+    reference_gpu = None
+    if world == 1 and not args.sharded and not args.no_reference_gpu and not args.graph_replay and args.ema == "config":
+        reference_gpu = run_sub_bench(["--impl", "reference-gpu", "--config", args.config, "--steps",
+                                       str(min(10, args.steps)), "--warmup", "3"], timeout=600)
+        reference_gpu = {k: reference_gpu.get(k) for k in ("value", "median_ms", "unit", "steps", "warmup", "clocks",
+                                                           "config", "unavailable") if k in reference_gpu}
     parity = sharded_parity(device, rank, dist) if distributed and not args.no_parity else None
 
     layers, d, dkv, dff, vocab = CONFIGS[args.config]
@@ -793,6 +916,8 @@ def run_gpu_arm(args) -> None:
             optimizer.round_elements = args.round_elements
         if args.adamw_first:
             optimizer.adamw_first = True
+        if args.costliest_first:
+            optimizer.costliest_second = False
         if args.apply_warps:
             optimizer.apply_warps = args.apply_warps
     else:
@@ -823,14 +948,6 @@ def run_gpu_arm(args) -> None:
         optimizer.graph_replay = True   # the stage hook is installed only while stages are timed
     else:
         _matrix_step.STAGE_HOOK = timer
-    real_adamw = _adamw.adamw_step
-
-    def timed_adamw(group, state, **kwargs):
-        with timer("adamw"):
-            real_adamw(group, state, **kwargs)
-
-    import dionw_b200.optimizer as optimizer_module
-    optimizer_module.adamw_step = timed_adamw
     if ema_kind == "cpu":
         # the snapshot kernel runs on the tracker's copy stream: the events land there
         real_stage = _native.ema_stage_pack
@@ -983,7 +1100,7 @@ def run_gpu_arm(args) -> None:
         "select": {"ms": stages.get("select")},
         "pack": {"ms": stages.get("pack"), "GB/s": gbs("bytes_pack", "pack", share)},
         "newton_schulz": {"ms": ns_ms, "TFLOP/s": ns_tflops, "by_operand": ns_by_shape},
-        "finish": {"ms": stages.get("finish"), "GB/s": gbs("bytes_finish", "finish", share)},
+        "finish": {"ms": stages.get("finish")},   # per-row scalars only: the row sums come from the last product
         "apply": {"ms": stages.get("apply"), "GB/s": gbs("bytes_apply", "apply")},
         "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
         "hbm_peak_GB/s": peaks["hbm_gbs"],
@@ -1001,6 +1118,28 @@ def run_gpu_arm(args) -> None:
         stage_report["ema_stage"] = {"ms": stages["ema_stage"], "GB/s": snapshot / stages["ema_stage"] / 1e6,
                                      "bound": "host link (device-to-host writes)", "bytes": snapshot}
     cpu = cpu_sample_step(args.config, 3, 1) if world == 1 and not args.no_cpu_baseline else None
+    # The Newton-Schulz microbenchmark (batches of 16 at the four shapes), after this arm's own numbers
+    # are taken and its memory is given back.
+    gram_ns = None
+    if reference_gpu is not None and args.config == "llama3-8b":
+        from dionw_b200 import _workspace
+
+        # give the device memory back whoever still refers to the tensors: storages are replaced
+        for p in model.parameters():
+            p.grad = None
+            p.data = torch.empty(0, device=device)
+        optimizer.state.clear()
+        optimizer._buckets = None
+        by_shape.clear()
+        pool.clear()
+        _workspace.release()
+        torch.cuda.empty_cache()
+        sub = run_sub_bench(["--config", "gram-ns", "--steps", "5", "--warmup", "3"], timeout=600)
+        gram_ns = sub if "unavailable" in sub else {
+            "shapes": [{k: row[k] for k in ("shape", "batch", "iteration_ms", "call_ms", "TFLOP/s", "executed_TFLOP/s",
+                                            "frac_of_burst_peak", "executed_frac_of_burst_peak", "orthogonality_error")
+                        if k in row} for row in sub.get("shapes", [])],
+            "clocks": sub.get("clocks"), "steps": sub.get("steps"), "warmup": sub.get("warmup")}
     line = {
         "metric": "optimizer_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
@@ -1011,7 +1150,8 @@ def run_gpu_arm(args) -> None:
                    "sharded_step": ({"overlap_apply": bool(optimizer.overlap_apply),
                                      "apply_warps": int(optimizer.apply_warps),
                                      "round_elements": int(optimizer.round_elements),
-                                     "adamw_first": bool(optimizer.adamw_first)} if distributed else None),
+                                     "adamw_first": bool(optimizer.adamw_first),
+                                     "costliest_second": bool(optimizer.costliest_second)} if distributed else None),
                    "ema": (None if ema is None else
                            f"{ema_kind.upper()} shadows, decay 0.9999, every step"
                            + (" (pinned host shadows, one snapshot kernel + host worker thread per step; the "
@@ -1036,6 +1176,8 @@ def run_gpu_arm(args) -> None:
                                     "an effective rate, not comparable with a hardware peak"},
         },
         "stages": stage_report,
+        "reference_gpu": reference_gpu,
+        "gram_ns": gram_ns,
         "parity": parity,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
@@ -1057,6 +1199,9 @@ def main() -> None:
     parser.add_argument("--impl", choices=("b200", "reference", "reference-gpu"), default="b200")
     parser.add_argument("--config", choices=sorted(CONFIGS) + ["gram-ns", "gemm-sustained"], default="llama3-8b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-reference-gpu", action="store_true",
+                        help="one GPU: do not time the reference's own GPU step and the Newton-Schulz microbenchmark "
+                             "in processes of their own before and after this arm")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
     parser.add_argument("--adamw-first", action="store_true",
                         help="sharded step: AdamW and its all-gathers before the first round (for comparison)")
@@ -1066,6 +1211,8 @@ def main() -> None:
                         help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
                              "counts only the steps that ran as launches")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
+    parser.add_argument("--costliest-first", action="store_true",
+                        help="sharded step: the costliest bucket's rounds first (for comparison; default: second)")
     parser.add_argument("--sharded", action="store_true",
                         help="one GPU: step with ShardedDion in a process group of one (its rounds, streams and "
                              "single-launch weight update) instead of Dion")

@@ -17,8 +17,9 @@ Stages (the arithmetic is that of src/dionw/_matrix_step.py:104-311):
 from __future__ import annotations
 
 import math
+import os
 from collections.abc import Callable, Sequence
-from contextlib import AbstractContextManager, nullcontext
+from contextlib import AbstractContextManager, contextmanager, nullcontext
 from dataclasses import dataclass
 from typing import Any
 
@@ -52,8 +53,25 @@ STAGE_HOOK: Callable[[str], AbstractContextManager[object]] | None = None
 CURRENT_RUN: tuple[int, int, int, int] | None = None
 
 
+# DIONW_NVTX=1 wraps every stage (accumulate, select, pack, newton_schulz, finish, apply, adamw)
+# in an NVTX range ``dionw/<stage>``, so a timeline profiler shows the kernel families of a step by
+# name.  Read once at import; off by default (a push and a pop per stage cost host time).
+_NVTX = os.environ.get("DIONW_NVTX", "0") not in ("", "0")
+
+
+@contextmanager
+def _nvtx_range(name: str, inner: AbstractContextManager[object]):
+    torch.cuda.nvtx.range_push(f"dionw/{name}")
+    try:
+        with inner:
+            yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
 def _stage(name: str) -> AbstractContextManager[object]:
-    return nullcontext() if STAGE_HOOK is None else STAGE_HOOK(name)
+    inner = nullcontext() if STAGE_HOOK is None else STAGE_HOOK(name)
+    return _nvtx_range(name, inner) if _NVTX else inner
 
 
 def run_elements(bucket: Bucket, position: int) -> int:

@@ -12,9 +12,15 @@
 // For them the scratch lives below, inside the library image, and this entry
 // point allocates nothing at all.
 //
-// The price is a fixed ceiling: kStaticScratchBytes per GPU, held from the
-// moment the library is loaded on that GPU until the process exits, whether or
-// not this entry point is ever called.  Problems that need more are refused.
+// The price is a fixed ceiling: kStaticScratchBytes per GPU, part of the library's
+// device image.  The CUDA runtime loads that image on a GPU when the library is first
+// used there (with lazy module loading, the default, as late as the first call of this
+// entry point), and it then stays until the process exits.  So the first call on a
+// device can fail with DIONW_ERR_CUDA in a process whose pools already hold nearly all
+// of that GPU's memory: make it during set-up, before the pools are filled.  Problems
+// that need more scratch than the ceiling are refused.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dionw {
@@ -29,18 +35,18 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 // Device address of g_static_scratch per device ordinal.  The symbol's name is
 // only a host-side handle: the address a kernel can use has to be asked for,
 // with the device in question current.
-void* g_scratch_address[64] = {nullptr};
+std::atomic<void*> g_scratch_address[64];   // zero-initialised; threads may race to fill a slot with the same value
 
 int scratch_for_current_device(void** out) {
   int device = 0;
   DIONW_CUDA(cudaGetDevice(&device));
   DIONW_REQUIRE(device >= 0 && device < 64, "newton_schulz_static: device ordinal %d is out of range", device);
-  if (g_scratch_address[device] == nullptr) {
-    void* address = nullptr;
+  void* address = g_scratch_address[device].load(std::memory_order_acquire);
+  if (address == nullptr) {
     DIONW_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
-    g_scratch_address[device] = address;
+    g_scratch_address[device].store(address, std::memory_order_release);
   }
-  *out = g_scratch_address[device];
+  *out = address;
   return DIONW_OK;
 }
 
@@ -53,6 +59,16 @@ extern "C" int dionw_newton_schulz_static(void* x, void* out, int64_t blocks, in
   const size_t need = dionw_newton_schulz_workspace_bytes(blocks, m, n, kind);
   if (need == 0) {
     set_error("newton_schulz_static: needs blocks > 0, m > 0, n > 0");
+    return DIONW_ERR_ARGUMENT;
+  }
+  // The ceiling is stated for operands stored with the smallest legal leading dimension, which is
+  // what dionw_newton_schulz_workspace_bytes assumes: a wider ldx would make the iteration's second
+  // operand, which has the same layout, larger than that figure.
+  if (ldx != (n + 7) / 8 * 8) {
+    set_error(
+        "newton_schulz_static: ldx must be n rounded up to a multiple of 8 (%lld for n = %lld), got %lld: the built-in "
+        "scratch is sized for that layout; use dionw_newton_schulz with a workspace of your own for padded operands",
+        (long long)((n + 7) / 8 * 8), (long long)n, (long long)ldx);
     return DIONW_ERR_ARGUMENT;
   }
   if (need > kStaticScratchBytes) {

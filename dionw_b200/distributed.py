@@ -160,6 +160,7 @@ class _ShardedCore(_DionCore):
         self._world = dist.get_world_size(process_group)
         self._rank = dist.get_rank(process_group)
         self._shared: list[_SharedBucket] | None = None
+        self._costliest: _SharedBucket | None = None
         self._round_streams: dict[torch.device, tuple[Any, Any]] = {}
         super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
                          weight_decay=weight_decay, eps=eps, matrix_update=matrix_update)
@@ -224,10 +225,18 @@ class _ShardedCore(_DionCore):
                     entry.pop(VARIANCE_STATE, None)
         # Costliest buckets first: the gathers and weight updates of the large rounds then have the
         # later rounds' work to hide behind, and the last gather of the step, which nothing
-        # hides, is the smallest.  Parameters are independent, so the order changes no result.
-        self._shared = sorted(
+        # hides, is the smallest.  With ``costliest_second`` the second costliest bucket goes before
+        # the costliest: the costliest bucket's gather (1.9 GB into every rank at the Llama-3-8B
+        # shapes on 8 ranks, about 2.7 ms) is then followed by a weight update AND a round's own
+        # work before its result is needed, instead of by one short round.  Parameters are
+        # independent, so the order changes no result.
+        ordered = sorted(
             shared.values(),
             key=lambda sb: -sum(newton_schulz_cost(sb.rows, sb.cols, sb.k, b) for b in sb.blocks))
+        self._costliest = ordered[0] if ordered else None
+        if self.costliest_second and len(ordered) >= 3:
+            ordered[0], ordered[1] = ordered[1], ordered[0]
+        self._shared = ordered
         self._buckets = [sb.local for sb in self._shared if sb.local is not None]
         return self._shared
 
@@ -271,9 +280,10 @@ class _ShardedCore(_DionCore):
     # time) and NCCL's kernels hold a few SMs while they run.  First in the step, they run beside the
     # Newton-Schulz of the first and costliest round, whose persistent products want every SM: on
     # 8 ranks that stage took 11.1 ms against 8.2 ms for the same blocks on a GPU of its own.  By
-    # default they are issued after the first round's Newton-Schulz, so they run beside its weight
-    # update and the later, small rounds instead.  The order changes no result.
+    # default they are issued after the Newton-Schulz of the costliest bucket's last round, so they
+    # run beside weight updates and the small rounds instead.  The order changes no result.
     adamw_first = False
+    costliest_second = True
 
     def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
         return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
@@ -304,9 +314,9 @@ class _ShardedCore(_DionCore):
                                                   torch.cuda.Stream(device=device))
         return pair
 
-    def _step_matrices(self, after_first_round: Callable[[], None] | None) -> None:
-        """Every round of the matrix step; ``after_first_round`` is called once the first round's
-        results are on their way to the other ranks."""
+    def _step_matrices(self, after_costliest: Callable[[], None] | None) -> None:
+        """Every round of the matrix step; ``after_costliest`` is called once the results of the
+        costliest bucket's last round are on their way to the other ranks."""
         import dionw_b200.optimizer as optimizer_module  # MAX_RUN_ELEMENTS is looked up at call time
 
         limit = min(optimizer_module.MAX_RUN_ELEMENTS, self.round_elements)
@@ -334,7 +344,8 @@ class _ShardedCore(_DionCore):
                 for members in per_rank:
                     sizes = [None if sb.params[i].grad is None else sb.blocks[i] * sb.k * sb.cols for i in members]
                     runs.append([[members[j] for j in run] for run in split_runs(sizes, limit)])
-                for t in range(max((len(r) for r in runs), default=0)):
+                rounds = max((len(r) for r in runs), default=0)
+                for t in range(rounds):
                     chosen = [r[t] if t < len(r) else [] for r in runs]
                     counts = [sum(sb.blocks[i] for i in c) for c in chosen]
                     slot = max(_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, selecting))[1]
@@ -356,9 +367,9 @@ class _ShardedCore(_DionCore):
                         work = self._all_gather(recv, send)
                     issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
                                     [[sb.blocks[i] for i in c] for c in chosen], sb, group)
-                    if round_id == 0 and after_first_round is not None:
+                    if sb is self._costliest and t == rounds - 1 and after_costliest is not None:
                         with torch.cuda.stream(side):
-                            after_first_round()
+                            after_costliest()
                     if pending is not None:
                         applied.append(self._apply_round(pending, compute, side))
                     pending = issued

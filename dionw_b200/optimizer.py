@@ -23,6 +23,7 @@ import torch
 from torch import Tensor
 from torch.optim import Optimizer
 
+from dionw_b200 import _matrix_step
 from dionw_b200._adamw import adamw_step, init_adamw_state
 from dionw_b200._buckets import Bucket, block_shape, build_buckets
 from dionw_b200._keys import (
@@ -388,7 +389,8 @@ class _DionCore(Optimizer):
     def _step_adamw_groups(self) -> None:
         for index, group in enumerate(self.param_groups):
             if RouteKind(group[ROUTE_KEY]) is RouteKind.ADAMW:
-                adamw_step(group, self.state, hyper=lambda device, index=index: self._adamw_hyper(index, device))
+                with _matrix_step._stage("adamw"):
+                    adamw_step(group, self.state, hyper=lambda device, index=index: self._adamw_hyper(index, device))
 
     # Optional two-stream step: the tensor-core part of run i (Newton-Schulz, on the
     # caller's stream) overlaps the HBM-bound parts of its neighbours on a side

@@ -149,16 +149,21 @@ int64_t dionw_newton_schulz_rowsq_parts(int64_t n);
  * this ABI without torch's allocator, a serving loop whose memory was budgeted at
  * start-up, a process whose device memory already belongs to a framework's pool,
  * a loop that may not stall on cudaMalloc/cudaFree.  The scratch is a fixed
- * DIONW_STATIC_SCRATCH_BYTES (64 MiB) array inside the library image, held on
- * every GPU the library is loaded on until the process exits; a problem whose
- * dionw_newton_schulz_workspace_bytes() exceeds it is refused with
- * DIONW_ERR_WORKSPACE.  The call allocates nothing.  Its first call on a device
- * looks the array's device address up (cudaGetSymbolAddress, with the current
- * device): make that call once per device during set-up, before any stream
- * capture is begun.  All calls on a device share the one array, which keeps
- * whatever the last call left in it (nothing needs clearing: each product writes
- * its output whole before it is read); two calls that overlap on the GPU, e.g.
- * on different streams, race on it.  Arguments as dionw_newton_schulz.
+ * DIONW_STATIC_SCRATCH_BYTES (64 MiB) array inside the library's device image: a
+ * GPU holds it from the moment the CUDA runtime loads the image there (with lazy
+ * module loading, as late as this entry's first call on that GPU) until the
+ * process exits.  A problem whose dionw_newton_schulz_workspace_bytes() exceeds
+ * it is refused with DIONW_ERR_WORKSPACE; the ceiling holds for operands with
+ * ldx == n rounded up to 8, any other ldx is refused with DIONW_ERR_ARGUMENT.
+ * The call allocates nothing.  Its first call on a device looks the array's
+ * device address up (cudaGetSymbolAddress, with the current device) and may be
+ * the call that loads the image, which fails with DIONW_ERR_CUDA if the GPU's
+ * memory is already full: make that call once per device during set-up, before
+ * memory pools are filled and before any stream capture is begun.  All calls on
+ * a device share the one array, which keeps whatever the last call left in it
+ * (nothing needs clearing: each product writes its output whole before it is
+ * read); two calls that overlap on the GPU, e.g. on different streams, race on
+ * it.  Arguments as dionw_newton_schulz (without the workspace and the row sums).
  * This entry has no counterpart in the reference. */
 #define DIONW_STATIC_SCRATCH_BYTES (64u << 20)
 int dionw_newton_schulz_static(void* x, void* out, int64_t blocks, int64_t m, int64_t n,

@@ -30,7 +30,7 @@ def _grads(net, step: int) -> None:
         p.grad = None if (step == 1 and i == 2) else (torch.randn(p.shape, generator=gen) * 1e-3).to(p.device)
 
 
-def _worker(rank: int, world: int, port: int, failures) -> None:
+def _worker(rank: int, world: int, port: int, failures, overlap: bool = False) -> None:
     import torch.distributed as dist
 
     import dionw_b200 as dionw
@@ -51,8 +51,11 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
 
         single_net, single = build(dionw.Dion)
         sharded_net, sharded = build(ShardedDion)
+        if overlap:   # the rounds on a high-priority stream, the weight updates beside them on another
+            sharded.overlap_apply = True
+            sharded.round_elements = 2 * 32 * 256
         owners = sharded.owners()
-        assert {0, 1} == set(owners.values())
+        assert set(range(world)) == set(owners.values())
         for step in range(3):
             _grads(single_net, step)
             _grads(sharded_net, step)
@@ -196,10 +199,14 @@ def _ema_worker(rank: int, world: int, port: int, failures, ema_device: str) -> 
 
 
 def _run_two_ranks(target, *extra) -> None:
+    _run_ranks(2, target, *extra)
+
+
+def _run_ranks(world: int, target, *extra) -> None:
     ctx = mp.get_context("spawn")
     failures = ctx.Queue()
     port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=target, args=(r, 2, port, failures, *extra)) for r in range(2)]
+    procs = [ctx.Process(target=target, args=(r, world, port, failures, *extra)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -209,8 +216,17 @@ def _run_two_ranks(target, *extra) -> None:
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_sharded_step_equals_single_gpu_step() -> None:
-    _run_two_ranks(_worker)
+@pytest.mark.parametrize("overlap", [False, True])
+def test_sharded_step_equals_single_gpu_step(overlap) -> None:
+    _run_two_ranks(_worker, overlap)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_sharded_step_in_a_group_of_one_equals_single_gpu_step(overlap) -> None:
+    """The sharded step's own machinery -- rounds, alternating arenas, one weight-update launch per
+    round, the gathered checkpoint, the resume -- on ONE GPU, in a process group of one: same bits
+    as ``Dion``, in line and with the updates overlapped on a second stream."""
+    _run_ranks(1, _worker, overlap)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

@@ -30,25 +30,38 @@ def _rel(a: torch.Tensor, b: torch.Tensor) -> float:
 
 
 def test_static_scratch_entry_matches_the_workspace_entry_twice() -> None:
+    """Two calls in a row (the second starts from the first one's leftovers), then the other
+    layouts of the scratch: a square block (standard iteration) and the bf16 kinds."""
     from dionw_b200 import _native
 
     _native.library()
-    for call, (blocks, m, n) in enumerate([(2, 512, 2048), (3, 256, 1024)]):
+    cases = [(2, 512, 2048, _native.NS_GRAM), (3, 256, 1024, _native.NS_GRAM), (2, 640, 640, _native.NS_GRAM),
+             (2, 384, 1000, _native.NS_POLAR_EXPRESS), (1, 512, 512, _native.NS_KELLER)]
+    for call, (blocks, m, n, kind) in enumerate(cases):
         x = _operand(blocks, m, n, seed=call)
-        need = _native.newton_schulz_workspace_bytes(blocks, m, n, _native.NS_GRAM)
+        if kind != _native.NS_GRAM:
+            x = x.bfloat16()
+        need = _native.newton_schulz_workspace_bytes(blocks, m, n, kind)
         assert 0 < need <= _native.STATIC_SCRATCH_BYTES
         expect = torch.empty(blocks, m, n, dtype=torch.bfloat16, device=DEV)
         workspace = torch.empty(need, dtype=torch.uint8, device=DEV)
-        _native.newton_schulz(x.clone(), expect, m, n, _native.NS_GRAM, workspace)
+        _native.newton_schulz(x.clone(), expect, m, n, kind, workspace)
         got = torch.empty(blocks, m, n, dtype=torch.bfloat16, device=DEV)
-        before = torch.cuda.memory_allocated()
-        _native.newton_schulz_static(x.clone(), got, m, n, _native.NS_GRAM)
+        operand = x.clone()
         torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()
+        _native.newton_schulz_static(operand, got, m, n, kind)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
         assert _native.device_status() == 0
         assert _rel(got.float(), expect.float()) <= 2e-3
         assert torch.equal(got, expect)
-        # one x.clone() came and went; nothing else was allocated through torch
-        assert torch.cuda.memory_allocated() <= before + x.numel() * 2
+        # nothing was allocated: not through torch, and not from the driver behind its back
+        # (the first call may be the one that loads the library's device image, scratch included)
+        assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            assert free_after >= free_before
 
 
 def test_static_scratch_entry_refuses_problems_beyond_its_ceiling() -> None:
@@ -59,3 +72,15 @@ def test_static_scratch_entry_refuses_problems_beyond_its_ceiling() -> None:
     x = torch.zeros(blocks, m, n, dtype=torch.float16, device=DEV)
     with pytest.raises(RuntimeError, match="built-in scratch holds"):
         _native.newton_schulz_static(x, x.view(torch.bfloat16), m, n, _native.NS_GRAM)
+
+
+def test_static_scratch_entry_refuses_padded_operands() -> None:
+    """The ceiling is stated for the smallest legal leading dimension; a wider one is refused by this
+    entry itself, with a message that names the built-in scratch."""
+    from dionw_b200 import _native
+
+    blocks, m, n = 1, 256, 1000
+    x = torch.zeros(blocks, m, 1024, dtype=torch.float16, device=DEV)[..., :1016]   # ldx = 1024, not 1000
+    with pytest.raises(ValueError, match="built-in"):
+        _native.newton_schulz_static(x, torch.empty(blocks, m, 1024, dtype=torch.bfloat16, device=DEV), m, n,
+                                     _native.NS_GRAM)
