@@ -916,8 +916,12 @@ def run_gpu_arm(args) -> None:
             optimizer.round_elements = args.round_elements
         if args.adamw_first:
             optimizer.adamw_first = True
+        if args.adamw_late:
+            optimizer.adamw_first = False
         if args.costliest_first:
             optimizer.costliest_second = False
+        if args.static_tiles:
+            _native.gemm_dynamic_tiles(False)
         if args.apply_warps:
             optimizer.apply_warps = args.apply_warps
     else:
@@ -1103,6 +1107,7 @@ def run_gpu_arm(args) -> None:
         "finish": {"ms": stages.get("finish")},   # per-row scalars only: the row sums come from the last product
         "apply": {"ms": stages.get("apply"), "GB/s": gbs("bytes_apply", "apply")},
         "adamw": {"ms": stages.get("adamw"), "GB/s": gbs("bytes_adamw", "adamw", share if distributed else 1.0)},
+        "gather_wait": {"ms": stages.get("gather_wait")},   # the stream blocked on an all-gather that has not landed yet
         "hbm_peak_GB/s": peaks["hbm_gbs"],
         "between_stages_ms": (whole_ms - sum(v for v in stages.values())) if whole_ms is not None else None,
     }
@@ -1151,7 +1156,8 @@ def run_gpu_arm(args) -> None:
                                      "apply_warps": int(optimizer.apply_warps),
                                      "round_elements": int(optimizer.round_elements),
                                      "adamw_first": bool(optimizer.adamw_first),
-                                     "costliest_second": bool(optimizer.costliest_second)} if distributed else None),
+                                     "costliest_second": bool(optimizer.costliest_second),
+                                     "dynamic_tiles": _native.gemm_dynamic_tiles()} if distributed else None),
                    "ema": (None if ema is None else
                            f"{ema_kind.upper()} shadows, decay 0.9999, every step"
                            + (" (pinned host shadows, one snapshot kernel + host worker thread per step; the "
@@ -1203,6 +1209,8 @@ def main() -> None:
                         help="one GPU: do not time the reference's own GPU step and the Newton-Schulz microbenchmark "
                              "in processes of their own before and after this arm")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--adamw-late", action="store_true",
+                        help="sharded step: AdamW and its all-gathers after the costliest bucket's rounds (for comparison)")
     parser.add_argument("--adamw-first", action="store_true",
                         help="sharded step: AdamW and its all-gathers before the first round (for comparison)")
     parser.add_argument("--ema", choices=("config", "none", "gpu", "cpu"), default="config",
@@ -1211,6 +1219,8 @@ def main() -> None:
                         help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
                              "counts only the steps that ran as launches")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
+    parser.add_argument("--static-tiles", action="store_true",
+                        help="sharded step: tensor-core products take their tiles in a fixed stride (for comparison)")
     parser.add_argument("--costliest-first", action="store_true",
                         help="sharded step: the costliest bucket's rounds first (for comparison; default: second)")
     parser.add_argument("--sharded", action="store_true",

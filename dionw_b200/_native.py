@@ -41,6 +41,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "dionw_device_status": (c_int, (POINTER(c_int),)),
     "dionw_launch_count": (c_int64, ()),
     "dionw_check_device": (c_int, ()),
+    "dionw_gemm_dynamic_tiles": (c_int, (c_int,)),
     "dionw_selftest_wait_timeout": (c_int, (c_int64, c_void_p, c_void_p)),
     "dionw_accumulate_row_l1_run": (c_int, (_PP, c_int, _I64P, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p)),
     "dionw_accumulate_copy_decay_run": (
@@ -171,6 +172,12 @@ def check_device() -> None:
     if status == -5:
         raise DeviceWaitError(f"dionw_b200: {last_error()} (code {status})")
     _check(status)
+
+
+def gemm_dynamic_tiles(on: bool | None = None) -> bool:
+    """Set (or with None only read) whether multi-wave tensor-core products draw their tiles from a
+    device counter instead of a fixed stride; returns the previous setting.  Process-wide."""
+    return bool(library().dionw_gemm_dynamic_tiles(-1 if on is None else int(on)))
 
 
 def selftest_wait_timeout(limit_us: int, gave_up: Tensor) -> None:

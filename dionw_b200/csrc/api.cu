@@ -26,6 +26,8 @@ void set_error(const char* fmt, ...) {
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+void reset_tile_counters();   // gemm.cu
+
 int* device_status_word() {
   static thread_local int* cached[64] = {nullptr};
   int dev = 0;
@@ -68,6 +70,7 @@ extern "C" int dionw_check_device(void) {
   const int st = dionw_device_status(&value);
   if (st != DIONW_OK) return st;
   if (value != 0) {
+    dionw::reset_tile_counters();
     dionw::set_error(
         "a bounded wait inside a kernel ran out (device status 0x%x): the results of the work queued since the "
         "last check are not to be trusted",

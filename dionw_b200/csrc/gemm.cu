@@ -2,7 +2,9 @@
 // product schedules built from them.
 #include <atomic>
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "gemm2_sm100.cuh"
 
@@ -105,6 +107,52 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const gemm::Param
   return check_cuda(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p), "gemm_kernel launch");
 }
 
+// ---- tile counters of the two-CTA kernel's dynamic hand-out ------------------------------------
+// One {next tile, pairs done} pair per (device, stream) that has launched a product with the dynamic
+// hand-out: launches of one stream run one after the other and each leaves its counters at zero,
+// launches of different streams may overlap and must not share.  The counters live in the library's
+// device image (zero at load); their address on a device is looked up once.
+constexpr int kCounterSlots = 1024;
+__device__ int g_tile_counters[kCounterSlots][2];
+
+std::mutex g_counter_mutex;
+std::map<std::pair<int, cudaStream_t>, int> g_counter_slot;   // guarded by g_counter_mutex
+int g_counter_next[kMaxDevices];                              // guarded by g_counter_mutex
+int* g_counter_base[kMaxDevices];                             // guarded by g_counter_mutex
+
+// Process-wide switch (dionw_gemm_dynamic_tiles): off by default.  A product launched with it on
+// draws its tiles from a counter; see gemm2_sm100.cuh.
+std::atomic<int> g_dynamic_tiles{-1};
+
+bool use_dynamic_tiles() {
+  int mode = g_dynamic_tiles.load(std::memory_order_relaxed);
+  if (mode < 0) {
+    const char* v = std::getenv("DIONW_GEMM_DYNAMIC_TILES");
+    mode = (v != nullptr && v[0] == '1') ? 1 : 0;
+    g_dynamic_tiles.store(mode, std::memory_order_relaxed);
+  }
+  return mode != 0;
+}
+
+// The counters of `stream` on the current device, or null when they cannot be had (the product then
+// takes its tiles in the fixed stride).
+int* tile_counters(cudaStream_t stream) {
+  const int device = current_device();
+  std::lock_guard<std::mutex> lock(g_counter_mutex);
+  if (g_counter_base[device] == nullptr) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_tile_counters) != cudaSuccess) return nullptr;
+    g_counter_base[device] = static_cast<int*>(address);
+  }
+  const auto key = std::make_pair(device, stream);
+  auto found = g_counter_slot.find(key);
+  if (found == g_counter_slot.end()) {
+    if (g_counter_next[device] >= kCounterSlots) return nullptr;
+    found = g_counter_slot.emplace(key, g_counter_next[device]++).first;
+  }
+  return g_counter_base[device] + 2 * found->second;
+}
+
 // Two-CTA tiles (clusters of two CTAs) unless the environment says DIONW_GEMM_CTA_PAIRS=0,
 // which selects the one-CTA kernel.
 bool use_cta_pairs() {
@@ -132,6 +180,9 @@ int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, 
   if (total == 0) return DIONW_OK;
   const int pairs_max = sm_count() / 2;
   const int pairs = total < pairs_max ? total : pairs_max;
+  // Tiles from a counter only where a pair takes more than one: a one-wave product gains nothing
+  // from it and would pay the hand-out's latency on its critical path.
+  p.tile_counter = (use_dynamic_tiles() && total > pairs) ? tile_counters(stream) : nullptr;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(unsigned(2 * pairs));
   config.blockDim = dim3(gemm2::kThreads);
@@ -282,6 +333,22 @@ extern "C" int dionw_batched_gemm(const void* a, int64_t lda, const void* b, int
   return dionw::batched_gemm(a, lda, m * lda, b, ldb, b_rows * ldb, b_is_nk != 0, cin, ldc, m * ldc, beta, out, ldo,
                              m * ldo, blocks, m, n, kdim, in_dtype, out_dtype, nullptr,
                              static_cast<cudaStream_t>(stream));
+}
+
+namespace dionw {
+// After a wait that ran out a product may have left its tile counters in any state: put them back to
+// zero on the current device (called by dionw_check_device when it reports a failure).
+void reset_tile_counters() {
+  void* address = nullptr;
+  if (cudaGetSymbolAddress(&address, g_tile_counters) == cudaSuccess)
+    cudaMemset(address, 0, sizeof(int) * 2 * kCounterSlots);
+}
+}  // namespace dionw
+
+extern "C" int dionw_gemm_dynamic_tiles(int on) {
+  const int before = dionw::use_dynamic_tiles() ? 1 : 0;
+  if (on >= 0) dionw::g_dynamic_tiles.store(on != 0 ? 1 : 0, std::memory_order_relaxed);
+  return before;
 }
 
 // ---------------------------------------------------------------------------

@@ -68,6 +68,51 @@ __device__ __forceinline__ void remote_arrive(uint32_t cluster_address) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
 }
 
+// Arrive with release semantics at cluster scope: what this thread wrote before (its own or the
+// peer's shared memory) is visible to a thread of either CTA that then observes the phase with an
+// acquire at cluster scope.  Used once per tile (the tile hand-out), never per stage.
+__device__ __forceinline__ void remote_arrive_release(uint32_t cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+
+__device__ __forceinline__ void remote_store_s32(uint32_t cluster_address, int value) {
+  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(cluster_address), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(gemm::smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait with the acquire at cluster scope (see gemm::mbar_wait for the protocol).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  uint64_t limit_ns) {
+  uint32_t spins = 0;
+  uint64_t start = 0;
+  while (!mbar_try_cluster(bar, parity)) {
+    if ((++spins & 1023u) == 0) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = gemm::global_ns();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicExch(status, gemm::kWaitCode);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // TMA load into this CTA's shared memory whose completion is signalled on a barrier of the
 // pair's leader CTA (the .cta_group::2 form allows the barrier to be the peer's).
 __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int c0,
@@ -154,6 +199,27 @@ __device__ __forceinline__ Tile sym_tile(int t, const Params& p) {
 }
 
 // ----------------------------------------------------------------------------
+// tile hand-out
+// ----------------------------------------------------------------------------
+// A pair takes its tiles either in a fixed stride (tile = pair, pair + pairs, ...: no shared state)
+// or from a counter in global memory, one atomicAdd per tile (Params::tile_counter non-null).  The
+// second form is for products that run beside other kernels (NCCL's, another stream's): a pair whose
+// CTAs become resident late, or not before the others are done, simply takes fewer tiles, where the
+// fixed stride makes the whole product wait for it.
+//
+// The leader CTA's producer thread draws the index and publishes it to every consumer of the pair
+// through a ring of kTileSlots entries kept in BOTH CTAs' shared memory: it writes the entry (its own
+// copy and, through the cluster's shared-memory window, the peer's), then arrives with release at
+// cluster scope on the slot's `tile_full` barrier of each CTA.  Consumers -- the leader's MMA thread,
+// the peer's producer thread and the eight epilogue warps of each CTA, 18 in all -- wait on their own
+// CTA's `tile_full` (acquire at cluster scope), read the entry and arrive on the LEADER's `tile_empty`
+// barrier of the slot; the producer reuses a slot after all 18 have done so.  -1 ends the pair's work.
+// When a pair has drawn its -1 it adds one to a second counter; the pair that brings that to the number
+// of pairs knows that nobody will draw again and clears both counters for the next launch on the stream.
+constexpr int kTileSlots = 4;
+constexpr uint32_t kTileConsumers = 2 * (1 + kEpilogueThreads / 32);
+
+// ----------------------------------------------------------------------------
 // the kernel (launched as clusters of two CTAs)
 // ----------------------------------------------------------------------------
 template <typename InT, typename OutT, bool kBMajorMN, bool kSym>
@@ -166,7 +232,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   uint64_t* empty_bar = full_bar + kStages;   // both: the pair's MMAs on this stage completed
   uint64_t* acc_full = empty_bar + kStages;   // [2] both: accumulator complete
   uint64_t* acc_empty = acc_full + 2;         // [2] leader only: both CTAs' epilogues drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* tile_full = acc_empty + 2;        // [kTileSlots] both: the slot's tile index is written
+  uint64_t* tile_empty = tile_full + kTileSlots;  // [kTileSlots] leader only: every consumer has read the slot
+  int* tile_ring = reinterpret_cast<int*>(tile_empty + kTileSlots);  // [kTileSlots]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_ring + kTileSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint16_t* mirror_stage = reinterpret_cast<uint16_t*>(smem + size_t(kStages) * kStageBytes + 256);
 
@@ -177,6 +246,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   const int pairs = gridDim.x >> 1;
   const int total_tiles = p.tiles_per_batch * p.batches;
   const int k_blocks = (p.kdim + kBK - 1) / kBK;
+  const bool dynamic = p.tile_counter != nullptr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -186,6 +256,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 2 * kEpilogueThreads);
+    }
+    for (int s = 0; s < kTileSlots; ++s) {
+      mbar_init(&tile_full[s], 1);
+      mbar_init(&tile_empty[s], kTileConsumers);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -200,12 +274,51 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   gemm::griddep_wait();     // set-up above overlaps the tail of the previous product; global memory from here on
   gemm::griddep_launch();
 
+  // The n-th tile of this pair for a consumer: its index, -1 when the pair is done, -2 when the wait
+  // gave up.  Called by ONE thread per consumer (the single-thread roles themselves, lane 0 of an
+  // epilogue warp), which also reports the slot as read.
+  const uint32_t leader_tile_empty = peer_address(&tile_empty[0], 0);
+  auto take_tile = [&](uint32_t n) -> int {
+    if (!dynamic) {
+      const long long t = (long long)pair + (long long)n * pairs;
+      return t < total_tiles ? int(t) : -1;
+    }
+    const uint32_t slot = n % kTileSlots;
+    if (!mbar_wait_cluster(&tile_full[slot], (n / kTileSlots) & 1u, abort_flag, p.status, p.wait_ns)) return -2;
+    const int t = tile_ring[slot];
+    remote_arrive_release(leader_tile_empty + slot * uint32_t(sizeof(uint64_t)));
+    return t;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += pairs) {
+      for (uint32_t n = 0; ok; ++n) {
+        int t;
+        if (dynamic && rank == 0) {
+          // draw the next tile and publish it to the pair
+          const uint32_t slot = n % kTileSlots;
+          if (!mbar_wait_cluster(&tile_empty[slot], ((n / kTileSlots) & 1u) ^ 1u, abort_flag, p.status, p.wait_ns)) break;
+          t = atomicAdd(p.tile_counter, 1);
+          if (t >= total_tiles) t = -1;
+          tile_ring[slot] = t;
+          remote_store_s32(peer_address(&tile_ring[slot], 1), t);
+          remote_arrive_release(peer_address(&tile_full[slot], 0));
+          remote_arrive_release(peer_address(&tile_full[slot], 1));
+          if (t < 0) {
+            // nobody of this pair draws again; the last pair to get here clears the counters
+            if (atomicAdd(p.tile_counter + 1, 1) == pairs - 1) {
+              p.tile_counter[0] = 0;
+              p.tile_counter[1] = 0;
+              __threadfence();
+            }
+          }
+        } else {
+          t = take_tile(n);
+        }
+        if (t < 0) break;
         const Tile tile = kSym ? gemm2::sym_tile(t, p) : gemm2::general_tile(t, p);
         const int m0 = tile.tm * kPairM + int(rank) * kBM;
         const int n0 = tile.tn * kBN + int(rank) * kHalfN;
@@ -237,9 +350,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     } else if (lane == 0) {
       // ------------------------------------------------------------ MMA issuer (leader)
       const uint32_t idesc = make_idesc2<InT, kBMajorMN>();
-      uint32_t it = 0, local = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += pairs, ++local) {
+      for (uint32_t local = 0; ok; ++local) {
+        if (take_tile(local) < 0) break;
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
@@ -273,9 +387,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const int first_chunk = (ew >> 2) * (kBN / 64);
     uint16_t* stage = mirror_stage + ew * 32 * kMirrorPitch;
     const uint32_t leader_empty[2] = {peer_address(&acc_empty[0], 0), peer_address(&acc_empty[1], 0)};
-    uint32_t local = 0;
     bool ok = true;
-    for (int t = pair; t < total_tiles && ok; t += pairs, ++local) {
+    for (uint32_t local = 0; ok; ++local) {
+      int t = 0;
+      if (lane == 0) t = take_tile(local);   // one lane waits, reads and reports; the warp follows it
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (t < 0) break;
       const Tile tile = kSym ? gemm2::sym_tile(t, p) : gemm2::general_tile(t, p);
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;

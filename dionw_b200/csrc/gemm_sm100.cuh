@@ -56,6 +56,7 @@ struct Params {
   int mirror_diagonal;   // symmetric schedule with B != A: also mirror inside the diagonal sub-blocks
   float* rowsq;          // nullable, general products only: [batches, m, rowsq_parts] partial row sums of out^2
   int rowsq_parts;       // = 2 * tiles_n: one partial per 128 columns, written once each, summed by the reader
+  int* tile_counter;     // two-CTA kernel: {next tile, pairs done} in global memory, or null for a fixed stride
   int* status;           // device status word (may be null: the code is then not recorded)
   uint64_t wait_ns;      // limit of every bounded wait, in nanoseconds of %globaltimer
 };

@@ -51,7 +51,7 @@ from dionw_b200.routing import RouteKind
 
 SHARD_KEY = "_dionw_shard"   # top-level entry of a per-rank checkpoint
 
-__all__ = ["SHARD_KEY", "ShardedDion", "assign_by_cost", "is_cut", "newton_schulz_cost", "shard_range", "split_runs"]
+__all__ = ["SHARD_KEY", "ShardedDion", "assign_by_cost", "bucket_order", "is_cut", "newton_schulz_cost", "shard_range", "split_runs"]
 
 # AdamW tensors at least this large are cut into per-rank element ranges.
 ADAMW_SHARD_MIN_ELEMENTS = 1 << 20
@@ -80,6 +80,16 @@ def assign_by_cost(costs: Sequence[float], world: int) -> list[int]:
         owner[i] = rank
         load[rank] += costs[i]
     return owner
+
+
+def bucket_order(costs: Sequence[float], costliest_second: bool) -> list[int]:
+    """Order in which the buckets' rounds are taken: by cost, highest first (ties to the lower
+    index); with ``costliest_second`` and at least three buckets the two costliest change places,
+    so that the costliest bucket's gather has a weight update and a round's own work to hide behind."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    if costliest_second and len(order) >= 3:
+        order[0], order[1] = order[1], order[0]
+    return order
 
 
 def split_runs(sizes: Sequence[int | None], limit: int) -> list[list[int]]:
@@ -159,6 +169,11 @@ class _ShardedCore(_DionCore):
         self._pg = process_group
         self._world = dist.get_world_size(process_group)
         self._rank = dist.get_rank(process_group)
+        if self._world > 1 and self.dynamic_tiles:
+            # The rounds' tensor-core products run beside NCCL's kernels, which hold a few SMs for
+            # milliseconds: with tiles drawn from a counter a product loses those SMs' share of its
+            # tiles instead of waiting for the SM pairs that cannot start (process-wide setting).
+            _native.gemm_dynamic_tiles(True)
         self._shared: list[_SharedBucket] | None = None
         self._costliest: _SharedBucket | None = None
         self._round_streams: dict[torch.device, tuple[Any, Any]] = {}
@@ -230,13 +245,10 @@ class _ShardedCore(_DionCore):
         # shapes on 8 ranks, about 2.7 ms) is then followed by a weight update AND a round's own
         # work before its result is needed, instead of by one short round.  Parameters are
         # independent, so the order changes no result.
-        ordered = sorted(
-            shared.values(),
-            key=lambda sb: -sum(newton_schulz_cost(sb.rows, sb.cols, sb.k, b) for b in sb.blocks))
-        self._costliest = ordered[0] if ordered else None
-        if self.costliest_second and len(ordered) >= 3:
-            ordered[0], ordered[1] = ordered[1], ordered[0]
-        self._shared = ordered
+        buckets = list(shared.values())
+        costs = [sum(newton_schulz_cost(sb.rows, sb.cols, sb.k, b) for b in sb.blocks) for sb in buckets]
+        self._costliest = buckets[max(range(len(costs)), key=lambda i: (costs[i], -i))] if buckets else None
+        self._shared = [buckets[i] for i in bucket_order(costs, self.costliest_second)]
         self._buckets = [sb.local for sb in self._shared if sb.local is not None]
         return self._shared
 
@@ -271,19 +283,26 @@ class _ShardedCore(_DionCore):
             self._step_matrices(adamw)
             if not done:   # no matrix round took place
                 adamw()
-        for work in gathers:
-            work.wait()
+        with _matrix_step._stage("gather_wait"):
+            for work in gathers:
+                work.wait()
         return loss
 
     # Where the AdamW tensors are updated and their ranges gathered.  Their all-gathers move 4 B per
     # AdamW element into every rank (3.7 GB at the Llama-3-8B shapes on 8 ranks, about 5 ms of link
-    # time) and NCCL's kernels hold a few SMs while they run.  First in the step, they run beside the
-    # Newton-Schulz of the first and costliest round, whose persistent products want every SM: on
-    # 8 ranks that stage took 11.1 ms against 8.2 ms for the same blocks on a GPU of its own.  By
-    # default they are issued after the Newton-Schulz of the costliest bucket's last round, so they
-    # run beside weight updates and the small rounds instead.  The order changes no result.
-    adamw_first = False
+    # time), NCCL runs the collectives of one communicator in the order they were issued, and its
+    # kernels hold a few SMs while they run.  Issued first in the step, these gathers are out of the
+    # way before the first large round's results queue up behind them, and they run beside the
+    # Newton-Schulz of the first rounds -- which is affordable because the products draw their tiles
+    # from a counter there (``dynamic_tiles``): with the fixed stride a product waits for the SM pairs
+    # NCCL's kernels keep from starting (4 GPUs, same call: Newton-Schulz 19.0 ms against 16.1 alone;
+    # 17.1 with the counter), and the step was faster with AdamW issued after the costliest round
+    # (36.7 ms); with the counter AdamW first wins (34.8 ms against 36.5).  ``adamw_first = False``
+    # issues them after the Newton-Schulz of the costliest bucket's last round.  The order changes
+    # no result.
+    adamw_first = True
     costliest_second = True
+    dynamic_tiles = True
 
     def _all_gather(self, out: Tensor, piece: Tensor) -> Any:
         return self._dist.all_gather_into_tensor(out, piece, group=self._pg, async_op=True)
@@ -384,7 +403,8 @@ class _ShardedCore(_DionCore):
         """Every rank's contribution of one round applied to this replica with one launch, on the side stream."""
         with torch.cuda.stream(side):
             if rnd.work is not None:
-                rnd.work.wait()             # the side stream waits for the gather
+                with _matrix_step._stage("gather_wait"):
+                    rnd.work.wait()         # the side stream waits for the gather
             elif side is not compute:
                 side.wait_stream(compute)   # one rank: the "received" data is the local result
             sb = rnd.bucket

@@ -68,6 +68,15 @@ int dionw_check_device(void);
  * No counterpart in the reference. */
 int dionw_selftest_wait_timeout(int64_t limit_us, int* gave_up, void* stream);
 
+/* How the two-CTA tensor-core products hand tiles to SM pairs: 0 (default) a
+ * fixed stride, 1 from a counter in device memory (one atomic per tile), so that a
+ * product running beside other kernels (NCCL's collectives in the sharded step)
+ * loses only the SMs those hold instead of waiting for the pairs that start late.
+ * Same arithmetic, same results.  Process-wide; on < 0 only queries.  Returns the
+ * previous setting.  DIONW_GEMM_DYNAMIC_TILES=1 sets the initial value.  No
+ * counterpart in the reference (its products are cuBLAS's and Triton's). */
+int dionw_gemm_dynamic_tiles(int on);
+
 /* ---- momentum passes ---------------------------------------------------- */
 
 /* M += G for every row of a run, plus per-row sum|M| (scores) and sum M^2.

@@ -153,3 +153,16 @@ def test_ema_ranges_gather_and_swap_over_gloo() -> None:
         p.join(120)
     assert failures.empty(), failures.get()
     assert all(p.exitcode == 0 for p in procs)
+
+
+def test_bucket_order_puts_the_costliest_second() -> None:
+    """Rounds go by cost; with three or more buckets the costliest goes second so that its gather,
+    the largest of the step, is followed by a weight update and a round before it is needed."""
+    from dionw_b200.distributed import bucket_order
+
+    costs = [3.2e12, 88.0e12, 0.13e12, 3.7e12]          # q/o, gate/up, k/v, down at the Llama-3-8B shapes
+    assert bucket_order(costs, costliest_second=False) == [1, 3, 0, 2]
+    assert bucket_order(costs, costliest_second=True) == [3, 1, 0, 2]
+    assert bucket_order([5.0, 9.0], costliest_second=True) == [1, 0]     # two buckets: plain order
+    assert bucket_order([2.0, 2.0, 2.0], costliest_second=False) == [0, 1, 2]
+    assert bucket_order([], costliest_second=True) == []

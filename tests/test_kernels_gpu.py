@@ -678,3 +678,42 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(native) ->
     expect = a.float() @ a.float().mT
     assert rel_l2(out[..., :300], expect) < 2e-3
     assert native.device_status() == 0
+
+
+def test_tiles_drawn_from_a_counter_give_the_same_bits(native) -> None:
+    """Multi-wave products with their tiles handed out by a device counter (the form used beside
+    NCCL's kernels in the sharded step) against the fixed stride: symmetric and general schedules,
+    several launches in a row on one stream (each launch must leave the counters at zero for the
+    next) and launches of two streams in flight together (each stream has counters of its own)."""
+    g = _gen(40)
+    a = (torch.randn(5, 1536, 512, generator=g) / 512**0.5).half().to(DEV)        # 5 x 21 = 105 tiles of the triangle
+    x = (torch.randn(3, 1024, 512, generator=g) / 512**0.5).half().to(DEV)
+    w = torch.randn(3, 512, 2560, generator=g).half().to(DEV)                     # 3 x 4 x 10 = 120 tiles
+
+    def products(stream=None):
+        sym = torch.empty(5, 1536, 1536, dtype=torch.float16, device=DEV)
+        gen = torch.empty(3, 1024, 2560, dtype=torch.float16, device=DEV)
+        with torch.cuda.stream(stream or torch.cuda.current_stream()):
+            for _ in range(3):
+                native.symmetric_product(a, sym)
+                native.batched_gemm(x, w, gen, b_is_nk=False)
+        return sym, gen
+
+    was = native.gemm_dynamic_tiles(False)
+    try:
+        expect = products()
+        torch.cuda.synchronize()
+        assert native.gemm_dynamic_tiles(True) is False
+        got = products()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        beside = products(side)
+        again = products()
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        for result in (got, beside, again):
+            for mine, want in zip(result, expect):
+                assert torch.equal(mine, want)
+        assert rel_l2(got[0], a.float() @ a.float().mT) < 2e-3
+    finally:
+        native.gemm_dynamic_tiles(was)
