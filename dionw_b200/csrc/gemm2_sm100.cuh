@@ -295,14 +295,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // The draw for tile n + 1 is issued before the loads of tile n: its latency hides behind them.
+      int drawn = (dynamic && rank == 0) ? atomicAdd(p.tile_counter, 1) : 0;
       for (uint32_t n = 0; ok; ++n) {
         int t;
         if (dynamic && rank == 0) {
-          // draw the next tile and publish it to the pair
+          // publish the tile drawn last to the pair
           const uint32_t slot = n % kTileSlots;
           if (!mbar_wait_cluster(&tile_empty[slot], ((n / kTileSlots) & 1u) ^ 1u, abort_flag, p.status, p.wait_ns)) break;
-          t = atomicAdd(p.tile_counter, 1);
-          if (t >= total_tiles) t = -1;
+          t = drawn < total_tiles ? drawn : -1;
+          if (t >= 0) drawn = atomicAdd(p.tile_counter, 1);
           tile_ring[slot] = t;
           remote_store_s32(peer_address(&tile_ring[slot], 1), t);
           remote_arrive_release(peer_address(&tile_full[slot], 0));

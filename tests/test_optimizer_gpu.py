@@ -220,11 +220,13 @@ def test_gate_up_shaped_block_matches_oracle(monkeypatch, full_products) -> None
     assert rel_l2(opt.state[net.weight]["momentum"], ref.buckets[0].momentum[0]) <= 1e-5
     # Two fp16 evaluations of the same product schedule (tensor cores here, the CPU's GEMM in the
     # oracle) leave row norms of this nearly square operand 1-2e-3 apart, with the products in
-    # full exactly as much as mirrored (3.3e-3 on the variance either way): the bound below is
-    # that spread, not a property of this implementation.  Well-conditioned blocks (config 1's
-    # 256 x 4096) meet 2e-3.
-    assert variance_error <= 5e-3
-    assert update_error <= 2e-2
+    # full exactly as much as mirrored (3.3e-3 on the variance either way).  That spread is between
+    # the two machines' GEMMs: against the reference's own step on the GPU the same block is within
+    # 1.6e-3 (mirrored) and 0.9e-3 (full), which is what the 2e-3 of the specification is checked
+    # against (tests/test_reference_gpu.py, the large blocks).  The bound here is the measured spread
+    # with a fifth of margin.
+    assert variance_error <= 4e-3
+    assert update_error <= 1e-2
 
 
 def test_70b_shaped_blocks_with_gpu_ema_match_oracle() -> None:
