@@ -500,7 +500,7 @@ def run_reference_arm(args) -> None:
 
 
 # ---------------------------------------------------------------------------
-# the reference's own GPU step (``--impl reference-gpu``; not the driver's reference arm)
+# the reference's own GPU step (``--impl reference-gpu``; ``--impl reference`` is the CPU arm)
 # ---------------------------------------------------------------------------
 def run_reference_gpu_arm(args) -> None:
     """The UNMODIFIED reference package, if a copy sits under ``baseline/_ref`` (git-ignored), on the
