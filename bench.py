@@ -922,6 +922,8 @@ def run_gpu_arm(args) -> None:
             optimizer.costliest_second = False
         if args.static_tiles:
             _native.gemm_dynamic_tiles(False)
+        if args.adamw_delay_rounds >= 0:
+            optimizer.adamw_delay_rounds = args.adamw_delay_rounds
         if args.apply_warps:
             optimizer.apply_warps = args.apply_warps
     else:
@@ -1156,6 +1158,7 @@ def run_gpu_arm(args) -> None:
                                      "apply_warps": int(optimizer.apply_warps),
                                      "round_elements": int(optimizer.round_elements),
                                      "adamw_first": bool(optimizer.adamw_first),
+                                     "adamw_delay_rounds": int(optimizer.adamw_delay_rounds),
                                      "costliest_second": bool(optimizer.costliest_second),
                                      "dynamic_tiles": _native.gemm_dynamic_tiles()} if distributed else None),
                    "ema": (None if ema is None else
@@ -1209,6 +1212,8 @@ def main() -> None:
                         help="one GPU: do not time the reference's own GPU step and the Newton-Schulz microbenchmark "
                              "in processes of their own before and after this arm")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--adamw-delay-rounds", type=int, default=-1,
+                        help="sharded step: rounds between the costliest bucket's last round and AdamW (default 1)")
     parser.add_argument("--adamw-late", action="store_true",
                         help="sharded step: AdamW and its all-gathers after the costliest bucket's rounds (for comparison)")
     parser.add_argument("--adamw-first", action="store_true",

@@ -289,18 +289,26 @@ class _ShardedCore(_DionCore):
         return loss
 
     # Where the AdamW tensors are updated and their ranges gathered.  Their all-gathers move 4 B per
-    # AdamW element into every rank (3.7 GB at the Llama-3-8B shapes on 8 ranks, about 5 ms of link
-    # time), NCCL runs the collectives of one communicator in the order they were issued, and its
-    # kernels hold a few SMs while they run.  Issued first in the step, these gathers are out of the
-    # way before the first large round's results queue up behind them, and they run beside the
-    # Newton-Schulz of the first rounds -- which is affordable because the products draw their tiles
-    # from a counter there (``dynamic_tiles``): with the fixed stride a product waits for the SM pairs
-    # NCCL's kernels keep from starting (4 GPUs, same call: Newton-Schulz 19.0 ms against 16.1 alone;
-    # 17.1 with the counter), and the step was faster with AdamW issued after the costliest round
-    # (36.7 ms); with the counter AdamW first wins (34.8 ms against 36.5).  ``adamw_first = False``
-    # issues them after the Newton-Schulz of the costliest bucket's last round.  The order changes
-    # no result.
+    # AdamW element into every rank (3.7 GB at the Llama-3-8B shapes on 8 ranks), NCCL runs the
+    # collectives of one communicator in the order they were issued, and its kernels need SMs: beside
+    # the tensor-core products they take about a fifth of them, beside the HBM-bound weight update,
+    # whose CTAs fill every SM's thread slots, they hardly get to run at all.  Issued first in the step
+    # (the default) the gathers are out of the queue before the first large round's results arrive
+    # behind them, and run beside the front stages and the Newton-Schulz of the first rounds, whose
+    # products draw their tiles from a counter (``dynamic_tiles``) and lose only the SMs NCCL holds.
+    # Measured, Llama-3-8B shapes, ms per step (Newton-Schulz stage; time the step waits for gathers):
+    #                                                       4 GPUs                8 GPUs
+    #   AdamW first, tiles from a counter (default)         34.8 (17.1; 0.2)      25.0 (10.1; 0.3)
+    #   AdamW first, fixed stride                           35.9 (19.0; 0.1)
+    #   right after the costliest bucket, fixed stride      36.7 (16.5; 3.3)      28.0 (8.5; 3.5)
+    #   one round after the costliest bucket, counter       37.3 (16.3; 3.3)
+    # (alone on a GPU the same blocks take 16.1 and 8.2 ms of Newton-Schulz).  A communicator of the
+    # AdamW gathers' own, limited to 2-8 CTAs so that it takes fewer SMs, was also measured on 4 GPUs:
+    # 8 CTAs 35.4 ms (no better), 4 CTAs 50 ms, 2 CTAs 81 ms (about 12 GB/s per CTA: the gathers no
+    # longer fit in the step).  ``adamw_first = False`` issues AdamW ``adamw_delay_rounds`` rounds
+    # after the costliest bucket's last round.  The order changes no result.
     adamw_first = True
+    adamw_delay_rounds = 1
     costliest_second = True
     dynamic_tiles = True
 
@@ -334,8 +342,8 @@ class _ShardedCore(_DionCore):
         return pair
 
     def _step_matrices(self, after_costliest: Callable[[], None] | None) -> None:
-        """Every round of the matrix step; ``after_costliest`` is called once the results of the
-        costliest bucket's last round are on their way to the other ranks."""
+        """Every round of the matrix step; ``after_costliest`` is called ``adamw_delay_rounds`` rounds
+        after the costliest bucket's last round, once that round's results are on their way."""
         import dionw_b200.optimizer as optimizer_module  # MAX_RUN_ELEMENTS is looked up at call time
 
         limit = min(optimizer_module.MAX_RUN_ELEMENTS, self.round_elements)
@@ -354,6 +362,7 @@ class _ShardedCore(_DionCore):
         pending: _Round | None = None
         applied: list[Any] = []  # applied[t]: event recorded on the side stream after round t's update
         round_id = 0
+        fire_round = -1          # the round after whose gather AdamW is issued
         with torch.cuda.stream(compute):
             for sb in shared:
                 group = self.param_groups[sb.group_index]
@@ -386,7 +395,9 @@ class _ShardedCore(_DionCore):
                         work = self._all_gather(recv, send)
                     issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
                                     [[sb.blocks[i] for i in c] for c in chosen], sb, group)
-                    if sb is self._costliest and t == rounds - 1 and after_costliest is not None:
+                    if sb is self._costliest and t == rounds - 1:
+                        fire_round = round_id + max(0, int(self.adamw_delay_rounds))
+                    if round_id == fire_round and after_costliest is not None:
                         with torch.cuda.stream(side):
                             after_costliest()
                     if pending is not None:
