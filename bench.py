@@ -930,6 +930,10 @@ def run_gpu_arm(args) -> None:
         optimizer = dionw.Dion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
     if args.no_overlap:
         optimizer.overlap_streams = False
+    if args.max_run_elements:
+        import dionw_b200.optimizer as optimizer_module_for_runs
+
+        optimizer_module_for_runs.MAX_RUN_ELEMENTS = args.max_run_elements
     gen = torch.Generator(device=device).manual_seed(1)
     param_bytes = sum(p.numel() * 4 for p in model.parameters())
     shared_grads = 2 * param_bytes > SHARED_GRADS_ABOVE
@@ -1224,6 +1228,8 @@ def main() -> None:
                         help="single GPU: replay the step from a CUDA graph (Dion.graph_replay); gpu_launches then "
                              "counts only the steps that ran as launches")
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
+    parser.add_argument("--max-run-elements", type=int, default=0,
+                        help="update elements one run orthogonalizes at once (default: the reference's 2^28)")
     parser.add_argument("--static-tiles", action="store_true",
                         help="sharded step: tensor-core products take their tiles in a fixed stride (for comparison)")
     parser.add_argument("--costliest-first", action="store_true",
