@@ -268,10 +268,10 @@ class _DionCore(Optimizer):
         base = len(values)
         for owner in owners:
             values.append(-step_size(owner, float(groups[owner.group_index]["lr"])) if isinstance(owner, Bucket) else 0.0)
-        devices = sorted({p.device for group in groups for p in group["params"] if p.is_cuda},
-                         key=lambda d: d.index or 0)
-        layout = (len(groups), tuple(id(o) for o in owners), tuple(devices))
+        layout = (len(groups), sum(len(group["params"]) for group in groups), tuple(id(o) for o in owners))
         if layout != self._scalar_layout:
+            devices = sorted({p.device for group in groups for p in group["params"] if p.is_cuda},
+                             key=lambda d: d.index or 0)
             self._scalar_tables = {d: torch.zeros(len(values), dtype=torch.float32, device=d) for d in devices}
             self._scalar_layout, self._scalar_values = layout, None
             for slot, owner in enumerate(owners):

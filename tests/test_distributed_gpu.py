@@ -229,6 +229,14 @@ def test_sharded_step_in_a_group_of_one_equals_single_gpu_step(overlap) -> None:
     _run_ranks(1, _worker, overlap)
 
 
+@pytest.mark.parametrize("ema_device", ["gpu", "cpu"])
+def test_sharded_ema_and_per_rank_checkpoints_in_a_group_of_one(ema_device) -> None:
+    """The EMA of ``ShardedDion``, its gathered checkpoint, the evaluation swap, the resume and the
+    per-rank checkpoint files (saved and loaded without a collective, refused for another rank) on
+    ONE GPU in a process group of one, against ``Dion``."""
+    _run_ranks(1, _ema_worker, ema_device)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("ema_device", ["gpu", "cpu"])
 def test_sharded_ema_equals_single_gpu_ema(ema_device) -> None:
