@@ -922,6 +922,10 @@ def run_gpu_arm(args) -> None:
             optimizer.costliest_second = False
         if args.static_tiles:
             _native.gemm_dynamic_tiles(False)
+        if args.no_fused_decay:
+            optimizer.fused_decay = False
+        if args.decay_rows_per_wait >= 0:
+            optimizer.decay_rows_per_wait = args.decay_rows_per_wait
         if args.adamw_delay_rounds >= 0:
             optimizer.adamw_delay_rounds = args.adamw_delay_rounds
         if args.apply_warps:
@@ -1164,7 +1168,9 @@ def run_gpu_arm(args) -> None:
                                      "adamw_first": bool(optimizer.adamw_first),
                                      "adamw_delay_rounds": int(optimizer.adamw_delay_rounds),
                                      "costliest_second": bool(optimizer.costliest_second),
-                                     "dynamic_tiles": _native.gemm_dynamic_tiles()} if distributed else None),
+                                     "dynamic_tiles": _native.gemm_dynamic_tiles(),
+                                     "fused_decay": bool(optimizer.fused_decay),
+                                     "decay_rows_per_wait": int(optimizer.decay_rows_per_wait)} if distributed else None),
                    "ema": (None if ema is None else
                            f"{ema_kind.upper()} shadows, decay 0.9999, every step"
                            + (" (pinned host shadows, one snapshot kernel + host worker thread per step; the "
@@ -1230,6 +1236,10 @@ def main() -> None:
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     parser.add_argument("--max-run-elements", type=int, default=0,
                         help="update elements one run orthogonalizes at once (default: the reference's 2^28)")
+    parser.add_argument("--no-fused-decay", action="store_true",
+                        help="sharded step: the weight update kernel decays every row itself (for comparison)")
+    parser.add_argument("--decay-rows-per-wait", type=int, default=-1,
+                        help="sharded step: rows of the decay job an epilogue warp may take per tile it waits for")
     parser.add_argument("--static-tiles", action="store_true",
                         help="sharded step: tensor-core products take their tiles in a fixed stride (for comparison)")
     parser.add_argument("--costliest-first", action="store_true",

@@ -280,9 +280,11 @@ def apply_result(result: RunResult, group: dict[str, Any]) -> None:
     apply_results([result], group)
 
 
-def apply_results(results: Sequence[RunResult], group: dict[str, Any], warps: int = 0) -> None:
+def apply_results(results: Sequence[RunResult], group: dict[str, Any], warps: int = 0,
+                  decay_job: Tensor | None = None) -> None:
     """Stage 5 for several results of one bucket shape (the contributions of every rank to a round
-    of the sharded step) in ONE launch per 64 weights.  ``warps`` sets the CTA size (0: the default)."""
+    of the sharded step) in ONE launch per 64 weights.  ``warps`` sets the CTA size (0: the default);
+    ``decay_job``: the job the round's products carried (its cursor says which rows are decayed)."""
     global CURRENT_RUN
     first = results[0]
     CURRENT_RUN = (sum(r.count for r in results), first.rows, first.k, first.cols)
@@ -315,7 +317,7 @@ def apply_results(results: Sequence[RunResult], group: dict[str, Any], warps: in
         _native.apply_round(targets, rows_per_tensor, o, rowmap or None, denom, scale,
                             ldo=first.orthogonal.stride(-2), rows=first.rows, k=first.k, cols=first.cols,
                             decay_factor=1.0 - lr * weight_decay, has_decay=weight_decay > 0.0,
-                            decay_device=first.decay_device, cta_warps=warps)
+                            decay_device=first.decay_device, cta_warps=warps, decay_job=decay_job)
     for param, target in zip(params, targets):
         if target is not param:
             param.copy_(target)

@@ -70,7 +70,11 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
                 c_void_p, c_int, c_void_p, c_void_p, c_void_p)),
     "dionw_apply_round": (
         c_int, (_PP, _I64P, _PP, _PP, _PP, _PP, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p, c_int,
-                c_int, c_void_p)),
+                c_int, c_void_p, c_void_p)),
+    "dionw_decay_job_bytes": (c_size_t, ()),
+    "dionw_decay_job_begin": (
+        c_int, (c_void_p, _PP, _PP, _I64P, c_int, c_int64, c_int64, c_float, c_void_p, c_int, c_void_p)),
+    "dionw_gemm_side_job": (None, (c_void_p,)),
     "dionw_write_scalars": (c_int, (c_void_p, POINTER(c_float), c_int64, c_void_p)),
     "dionw_apply_run": (
         c_int, (_PP, _I64P, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
@@ -308,7 +312,7 @@ def apply_run(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Tens
 def apply_round(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Sequence[int],
                 rowmap: Sequence[int] | None, denom: Sequence[int], scale: Sequence[int], *, ldo: int,
                 rows: int, k: int, cols: int, decay_factor: float, has_decay: bool,
-                decay_device: Tensor | None = None, cta_warps: int = 0) -> None:
+                decay_device: Tensor | None = None, cta_warps: int = 0, decay_job: Tensor | None = None) -> None:
     """The weight update of tensors whose update rows lie in different buffers, in one launch:
     ``o[i]``, ``rowmap[i]``, ``denom[i]``, ``scale[i]`` are the device addresses of the first block
     of tensor ``i`` (bf16 rows, int32 row map, fp32 divisors, fp32 block scales)."""
@@ -316,7 +320,30 @@ def apply_round(weights: Sequence[Tensor], rows_per_tensor: Sequence[int], o: Se
     _check(library().dionw_apply_round(
         _ptr_array(weights), _i64_array(rows_per_tensor), (c_void_p * n)(*o),
         None if rowmap is None else (c_void_p * n)(*rowmap), (c_void_p * n)(*denom), (c_void_p * n)(*scale), n, ldo,
-        rows, k, cols, decay_factor, _ptr(decay_device), int(has_decay), cta_warps, _stream(weights[0])))
+        rows, k, cols, decay_factor, _ptr(decay_device), int(has_decay), cta_warps, _ptr(decay_job),
+        _stream(weights[0])))
+
+
+def decay_job_bytes() -> int:
+    """Bytes of device memory one decay job takes."""
+    return int(library().dionw_decay_job_bytes())
+
+
+def decay_job_begin(job: Tensor, weights: Sequence[Tensor], rowmap: Sequence[int], rows_per_tensor: Sequence[int], *,
+                    rows: int, cols: int, decay_factor: float, decay_device: Tensor | None = None,
+                    rows_per_wait: int = 2) -> None:
+    """Write the decay job of a round into ``job`` (a byte tensor of ``decay_job_bytes()``): the
+    round's weights in the order ``apply_round`` will get them, ``rowmap[i]`` the device address of
+    tensor ``i``'s int32 row map."""
+    n = len(weights)
+    _check(library().dionw_decay_job_begin(
+        job.data_ptr(), _ptr_array(weights), (c_void_p * n)(*rowmap), _i64_array(rows_per_tensor), n, rows, cols,
+        decay_factor, _ptr(decay_device), rows_per_wait, _stream(job)))
+
+
+def gemm_side_job(job: Tensor | None) -> None:
+    """Products launched by this thread from now on carry ``job`` (None: no job)."""
+    library().dionw_gemm_side_job(_ptr(job))
 
 
 def write_scalars(dst: Tensor, values: Sequence[float]) -> None:

@@ -153,6 +153,9 @@ int* tile_counters(cudaStream_t stream) {
   return g_counter_base[device] + 2 * found->second;
 }
 
+// The streaming job (decay_job.cuh) that products launched by this thread carry, or null.
+thread_local DecayJob* t_side_job = nullptr;
+
 // Two-CTA tiles (clusters of two CTAs) unless the environment says DIONW_GEMM_CTA_PAIRS=0,
 // which selects the one-CTA kernel.
 bool use_cta_pairs() {
@@ -183,6 +186,8 @@ int launch2(const CUtensorMap& map_a, const CUtensorMap& map_b, gemm::Params p, 
   // Tiles from a counter only where a pair takes more than one: a one-wave product gains nothing
   // from it and would pay the hand-out's latency on its critical path.
   p.tile_counter = (use_dynamic_tiles() && total > pairs) ? tile_counters(stream) : nullptr;
+  // The streaming job rides on products whose main loop is long enough to hide a row behind it.
+  p.job = (p.kdim >= 24 * gemm2::kBK) ? t_side_job : nullptr;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(unsigned(2 * pairs));
   config.blockDim = dim3(gemm2::kThreads);
@@ -344,6 +349,8 @@ void reset_tile_counters() {
     cudaMemset(address, 0, sizeof(int) * 2 * kCounterSlots);
 }
 }  // namespace dionw
+
+extern "C" void dionw_gemm_side_job(void* job) { dionw::t_side_job = static_cast<dionw::DecayJob*>(job); }
 
 extern "C" int dionw_gemm_dynamic_tiles(int on) {
   const int before = dionw::use_dynamic_tiles() ? 1 : 0;

@@ -401,6 +401,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const Tile tile = kSym ? gemm2::sym_tile(t, p) : gemm2::general_tile(t, p);
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
+      if (p.job != nullptr) {
+        // The accumulator of this tile is still being summed: take rows of the streaming job
+        // meanwhile, at most `per_wait` of them, one at a time, looking at the barrier in between.
+        const int limit = p.job->per_wait;
+        for (int taken = 0; taken < limit; ++taken) {
+          long long row = -1;
+          if (lane == 0 && !mbar_try(&acc_full[acc], acc_phase)) row = atomicAdd(&p.job->cursor, 1);
+          row = __shfl_sync(0xffffffffu, row, 0);
+          if (row < 0 || row >= p.job->total_rows) break;
+          decay_job_row(p.job, row, lane);
+        }
+      }
       if (!epilogue_tile<InT, OutT, kSym>(p, tile.batch, tile.tm * kPairM + int(rank) * kBM, tile.tn * kBN,
                                           tmem_base + acc * uint32_t(kBN), &acc_full[acc], acc_phase, abort_flag,
                                           stage, sub, lane, first_chunk)) {

@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "decay_job.cuh"
 
 namespace dionw {
 namespace gemm {
@@ -57,6 +58,7 @@ struct Params {
   float* rowsq;          // nullable, general products only: [batches, m, rowsq_parts] partial row sums of out^2
   int rowsq_parts;       // = 2 * tiles_n: one partial per 128 columns, written once each, summed by the reader
   int* tile_counter;     // two-CTA kernel: {next tile, pairs done} in global memory, or null for a fixed stride
+  DecayJob* job;         // two-CTA kernel: streaming job the epilogue warps work on while they wait, or null
   int* status;           // device status word (may be null: the code is then not recorded)
   uint64_t wait_ns;      // limit of every bounded wait, in nanoseconds of %globaltimer
 };

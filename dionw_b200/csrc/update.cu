@@ -3,6 +3,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "decay_job.cuh"
 
 namespace dionw {
 namespace {
@@ -130,10 +131,17 @@ struct ApplyTable {
 // register count is held down (32-bit indices inside a row, the update's scale folded once per row).
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, 6)
 apply_run_kernel(const ApplyTable tab, long long total_rows, int ldo, int rows, int k, int cols, float decay_host,
-                 const float* __restrict__ decay_device, bool has_decay, bool vec) {
+                 const float* __restrict__ decay_device, bool has_decay, bool vec, const DecayJob* __restrict__ job) {
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;   // one row per warp; the launch chooses the CTA size
   const long long stride = (long long)gridDim.x * warps;
+  // Rows below this were offered to the tensor-core kernels' streaming job: the unselected ones among
+  // them are decayed already.
+  long long decayed_below = 0;
+  if (job != nullptr) {
+    const long long handed_out = job->cursor;
+    decayed_below = handed_out < total_rows ? handed_out : total_rows;
+  }
   for (long long local = (long long)blockIdx.x * warps + (threadIdx.x >> 5); local < total_rows; local += stride) {
     int lo = 0, hi = tab.n - 1;
     while (lo < hi) {
@@ -144,7 +152,7 @@ apply_run_kernel(const ApplyTable tab, long long total_rows, int ldo, int rows, 
     const int b = int(row / rows);
     const int32_t* rowmap = tab.e[lo].rowmap;
     const int pos = rowmap ? rowmap[row] : int(row - (long long)b * rows);
-    if (pos < 0 && !has_decay) continue;
+    if (pos < 0 && (!has_decay || local < decayed_below)) continue;
     float* __restrict__ w = tab.e[lo].w + row * cols;
     const float decay_factor = decay_device != nullptr ? __ldg(decay_device) : decay_host;
     if (pos < 0) {
@@ -437,7 +445,7 @@ extern "C" int dionw_apply_round(void* const* weights, const int64_t* rows_per_t
                                  const int32_t* const* rowmap, const float* const* denom, const float* const* scale,
                                  int n_tensors, int64_t ldo, int64_t rows, int64_t k, int64_t cols,
                                  float decay_factor, const float* decay_device, int has_decay, int cta_warps,
-                                 void* stream_ptr) {
+                                 const void* decay_job, void* stream_ptr) {
   DIONW_REQUIRE(n_tensors > 0 && rows > 0 && k > 0 && cols > 0, "apply_round: empty round");
   DIONW_REQUIRE(rows < (1ll << 31) && cols < (1ll << 31) && ldo < (1ll << 31), "apply_round: a block dimension exceeds 2^31");
   DIONW_REQUIRE(cta_warps >= 0 && cta_warps <= kWarpsPerBlock, "apply_round: cta_warps must be 0 (default) .. %d",
@@ -447,6 +455,8 @@ extern "C" int dionw_apply_round(void* const* weights, const int64_t* rows_per_t
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   bool vec = cols % 4 == 0 && ldo % 4 == 0;
   for (int i = 0; i < n_tensors; ++i) vec = vec && aligned16(weights[i]) && (reinterpret_cast<uintptr_t>(o[i]) & 7u) == 0;
+  DIONW_REQUIRE(decay_job == nullptr || n_tensors <= kTable,
+                "apply_round: a decay job covers at most %d tensors, the round has %d", kTable, n_tensors);
   for (int start = 0; start < n_tensors; start += kTable) {
     ApplyTable tab;
     tab.n = (n_tensors - start < kTable) ? n_tensors - start : kTable;
@@ -464,7 +474,8 @@ extern "C" int dionw_apply_round(void* const* weights, const int64_t* rows_per_t
       long long grid = (acc + warps - 1) / warps;
       if (grid > 0x7FFFFFFFll) grid = 0x7FFFFFFFll;   // the kernel walks the rows with a stride
       apply_run_kernel<<<unsigned(grid), warps * 32, 0, stream>>>(tab, acc, int(ldo), int(rows), int(k), int(cols),
-                                                                  decay_factor, decay_device, has_decay != 0, vec);
+                                                                  decay_factor, decay_device, has_decay != 0, vec,
+                                                                  static_cast<const DecayJob*>(decay_job));
       const int st = launch_status("apply_run_kernel");
       if (st != DIONW_OK) return st;
     }
@@ -493,7 +504,73 @@ extern "C" int dionw_apply_run(void* const* weights, const int64_t* rows_per_ten
     row += rows_per_tensor[i];
   }
   return dionw_apply_round(weights, rows_per_tensor, o_of, rowmap ? map_of : nullptr, denom_of, scale_of, n_tensors,
-                           ldo, rows, k, cols, decay_factor, nullptr, has_decay, 0, stream_ptr);
+                           ldo, rows, k, cols, decay_factor, nullptr, has_decay, 0, nullptr, stream_ptr);
+}
+
+// ---------------------------------------------------------------------------
+// the decay job of a round (decay_job.cuh)
+// ---------------------------------------------------------------------------
+namespace dionw {
+namespace {
+struct JobInit {
+  float* w[kJobTensors];
+  const int32_t* rowmap[kJobTensors];
+  long long row_end[kJobTensors];
+};
+
+__global__ void decay_job_begin_kernel(DecayJob* job, const JobInit init, int n, int rows, int cols, int vec,
+                                       int per_wait, long long total_rows, float decay_host,
+                                       const float* decay_device) {
+  const int i = threadIdx.x;
+  if (i < n) {
+    job->w[i] = init.w[i];
+    job->rowmap[i] = init.rowmap[i];
+    job->row_end[i] = init.row_end[i];
+  }
+  if (i == 0) {
+    job->n = n;
+    job->rows = rows;
+    job->cols = cols;
+    job->vec = vec;
+    job->per_wait = per_wait;
+    job->cursor = 0;
+    job->total_rows = total_rows;
+    job->decay_host = decay_host;
+    job->decay_device = decay_device;
+  }
+}
+}  // namespace
+}  // namespace dionw
+
+extern "C" size_t dionw_decay_job_bytes(void) { return sizeof(dionw::DecayJob); }
+
+extern "C" int dionw_decay_job_begin(void* job, void* const* weights, const int32_t* const* rowmap,
+                                     const int64_t* rows_per_tensor, int n_tensors, int64_t rows, int64_t cols,
+                                     float decay_factor, const float* decay_device, int rows_per_wait,
+                                     void* stream_ptr) {
+  DIONW_REQUIRE(job != nullptr && (reinterpret_cast<uintptr_t>(job) & 15u) == 0, "decay_job_begin: job must be 16-byte aligned device memory");
+  DIONW_REQUIRE(n_tensors > 0 && n_tensors <= kJobTensors, "decay_job_begin: 1 .. %d tensors (got %d)", kJobTensors,
+                n_tensors);
+  DIONW_REQUIRE(weights && rowmap && rows_per_tensor && rows > 0 && cols > 0 && cols < (1ll << 31) && rows < (1ll << 31),
+                "decay_job_begin: bad shape");
+  DIONW_REQUIRE(rows_per_wait >= 0 && rows_per_wait <= 64, "decay_job_begin: rows_per_wait must be 0 .. 64");
+  JobInit init;
+  long long acc = 0;
+  bool vec = cols % 4 == 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    DIONW_REQUIRE(rowmap[i] != nullptr, "decay_job_begin: tensor %d has no row map (every row is selected: nothing to decay ahead)", i);
+    DIONW_REQUIRE(rows_per_tensor[i] >= 0 && rows_per_tensor[i] % rows == 0, "decay_job_begin: tensor %d has %lld rows, not a multiple of %lld", i, (long long)rows_per_tensor[i], (long long)rows);
+    acc += rows_per_tensor[i];
+    init.w[i] = static_cast<float*>(weights[i]);
+    init.rowmap[i] = rowmap[i];
+    init.row_end[i] = acc;
+    vec = vec && aligned16(weights[i]);
+  }
+  DIONW_REQUIRE(acc < (1ll << 30), "decay_job_begin: too many rows for one job");
+  decay_job_begin_kernel<<<1, kJobTensors, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<DecayJob*>(job), init, n_tensors, int(rows), int(cols), vec ? 1 : 0, rows_per_wait, acc, decay_factor,
+      decay_device);
+  return launch_status("decay_job_begin_kernel");
 }
 
 extern "C" int dionw_adamw_multi(void* const* params, const void* const* grads, void* const* exp_avg,

@@ -153,6 +153,7 @@ class _Round:
     blocks: list[list[int]]
     bucket: _SharedBucket
     group: dict[str, Any]
+    job: Tensor | None = None   # the decay job the round's products carried
 
 
 class _ShardedCore(_DionCore):
@@ -169,6 +170,14 @@ class _ShardedCore(_DionCore):
         self._pg = process_group
         self._world = dist.get_world_size(process_group)
         self._rank = dist.get_rank(process_group)
+        # The rounds' row maps travel on a communicator of their own: NCCL runs the collectives of one
+        # communicator in the order they were issued, and a 60 KB exchange that the round's products
+        # wait for must not queue behind the previous round's results or AdamW's ranges (2 GPUs,
+        # one communicator: 6.9 ms of a 58.9 ms step spent there).  Every rank issues the same
+        # collectives in the same order on both communicators.
+        self._pg_maps = process_group
+        if self._world > 1 and self.fused_decay:
+            self._pg_maps = dist.new_group(ranks=dist.get_process_group_ranks(process_group or dist.group.WORLD))
         if self._world > 1 and self.dynamic_tiles:
             # The rounds' tensor-core products run beside NCCL's kernels, which hold a few SMs for
             # milliseconds: with tiles drawn from a counter a product loses those SMs' share of its
@@ -383,10 +392,22 @@ class _ShardedCore(_DionCore):
                         compute.wait_event(applied[round_id - 2])
                     name = f"run{round_id % 2}"
                     _workspace.arena(device, slot, name)
+                    ctx = None
                     if chosen[me]:
                         local_index = {id(p): j for j, p in enumerate(sb.local.params)}
                         positions = [local_index[id(sb.params[i])] for i in chosen[me]]
-                        _matrix_step.prepare_run(sb.local, positions, group, arena=name)
+                        ctx = _matrix_step.open_run(sb.local, positions, group, arena=name)
+                        _matrix_step.run_front(ctx)
+                    job = None
+                    if (self.fused_decay and selecting and compute is main and float(group["weight_decay"]) > 0.0
+                            and 0 < sum(len(c) for c in chosen) <= 64):
+                        job = self._begin_decay_job(sb, group, chosen, counts, slot, name, round_id, device)
+                    if ctx is not None:
+                        _native.gemm_side_job(job)
+                        try:
+                            _matrix_step.run_core(ctx)
+                        finally:
+                            _native.gemm_side_job(None)
                     send = _workspace.arena(device, slot, name)[:slot]
                     if world == 1:
                         recv, work = send, None
@@ -394,7 +415,7 @@ class _ShardedCore(_DionCore):
                         recv = _workspace.arena(device, slot * world, f"recv{round_id % 2}")[: slot * world]
                         work = self._all_gather(recv, send)
                     issued = _Round(work, recv, slot, counts, [[sb.params[i] for i in c] for c in chosen],
-                                    [[sb.blocks[i] for i in c] for c in chosen], sb, group)
+                                    [[sb.blocks[i] for i in c] for c in chosen], sb, group, job)
                     if sb is self._costliest and t == rounds - 1:
                         fire_round = round_id + max(0, int(self.adamw_delay_rounds))
                     if round_id == fire_round and after_costliest is not None:
@@ -409,6 +430,54 @@ class _ShardedCore(_DionCore):
         if compute is not main:
             main.wait_stream(compute)
             main.wait_stream(side)
+
+    # The decoupled decay of the rows a round does NOT select (three quarters of the 8 B per weight
+    # element that every rank spends on the update) depends on nothing but the row maps, which exist
+    # after `select`, before the round's first product.  With ``fused_decay`` the ranks exchange
+    # their row maps right there (a small all-gather), describe the round's weights in a decay job
+    # (csrc/decay_job.cuh), and the round's tensor-core products carry it: their epilogue warps decay
+    # rows while they wait for their accumulators.  The update kernel then skips what the job's
+    # cursor covers.  Same multiplication, once per element: bit-identical weights.
+    fused_decay = True
+    decay_rows_per_wait = 2
+
+    def _begin_decay_job(self, sb: _SharedBucket, group: dict[str, Any], chosen: list[list[int]], counts: list[int],
+                         slot: int, name: str, round_id: int, device: torch.device) -> Tensor | None:
+        world, me = self._world, self._rank
+        plans = [_workspace.layout(_matrix_step.exchange_plan(c, sb.rows, sb.k, sb.cols, True))[0]["rowmap"] if c else (0, 0)
+                 for c in counts]
+        piece_bytes = max(nbytes for _, nbytes in plans)
+        piece_bytes = (piece_bytes + 255) // 256 * 256
+        own_offset = plans[me][0]
+        send = _workspace.arena(device, slot, name)
+        if world == 1:
+            maps = send[own_offset:own_offset + piece_bytes]
+            stride = 0
+        else:
+            maps = _workspace.arena(device, piece_bytes * world, f"rowmaps{round_id % 2}")[: piece_bytes * world]
+            # the piece may run past this rank's own row maps into what follows them in the arena
+            # (the largest contribution's layout bounds it): the other ranks never look there
+            self._dist.all_gather_into_tensor(maps, send[own_offset:own_offset + piece_bytes], group=self._pg_maps)
+            stride = piece_bytes
+        weights: list[Tensor] = []
+        rowmaps: list[int] = []
+        rows_per_tensor: list[int] = []
+        base = maps.data_ptr()
+        for rank in range(world):
+            block = 0
+            for i in chosen[rank]:
+                weights.append(sb.params[i])
+                rowmaps.append(base + rank * stride + block * sb.rows * 4)
+                rows_per_tensor.append(sb.blocks[i] * sb.rows)
+                block += sb.blocks[i]
+        if not all(w.is_contiguous() for w in weights):
+            return None   # a strided weight is updated through a packed copy: nothing to decay in place
+        job = _workspace.arena(device, _native.decay_job_bytes(), f"decayjob{round_id % 2}")
+        lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
+        _native.decay_job_begin(job, weights, rowmaps, rows_per_tensor, rows=sb.rows, cols=sb.cols,
+                                decay_factor=1.0 - lr * weight_decay, decay_device=sb.decay_device,
+                                rows_per_wait=self.decay_rows_per_wait)
+        return job
 
     def _apply_round(self, rnd: _Round, compute: Any, side: Any) -> Any:
         """Every rank's contribution of one round applied to this replica with one launch, on the side stream."""
@@ -433,7 +502,7 @@ class _ShardedCore(_DionCore):
                     denom=got["denom"], scale=got["scale"], decay_device=sb.decay_device))
             if results:
                 _matrix_step.apply_results(results, rnd.group,
-                                           warps=self.apply_warps if side is not compute else 0)
+                                           warps=self.apply_warps if side is not compute else 0, decay_job=rnd.job)
             done = torch.cuda.Event()
             done.record(side)
         return done

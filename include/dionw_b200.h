@@ -248,7 +248,31 @@ int dionw_apply_round(void* const* weights, const int64_t* rows_per_tensor,
                       const void* const* o, const int32_t* const* rowmap,
                       const float* const* denom, const float* const* scale, int n_tensors,
                       int64_t ldo, int64_t rows, int64_t k, int64_t cols, float decay_factor,
-                      const float* decay_device, int has_decay, int cta_warps, void* stream);
+                      const float* decay_device, int has_decay, int cta_warps,
+                      const void* decay_job, void* stream);
+
+/* A decay job: the decoupled decay of the UNSELECTED rows of a round's weights,
+ * done by the tensor-core kernels' epilogue warps while they wait for their
+ * accumulators, so that it runs beside the Newton-Schulz of the round instead
+ * of after it (no counterpart in the reference, which decays with one
+ * elementwise multiply, src/dionw/_matrix_step.py:280).  `job` is
+ * dionw_decay_job_bytes() of 16-byte aligned device memory that must stay
+ * untouched until the dionw_apply_round that is given the same pointer has run;
+ * weights / rowmap / rows_per_tensor describe the round's tensors in the order
+ * dionw_apply_round will get them (at most 64; every tensor needs a row map).
+ * dionw_decay_job_begin writes the job (stream-ordered).  dionw_gemm_side_job(job)
+ * makes the products launched by the calling thread from then on carry it
+ * (NULL: none): a waiting epilogue warp draws up to rows_per_wait rows per tile
+ * from the job's cursor and multiplies the unselected ones by the decay factor.
+ * dionw_apply_round(..., decay_job = job, ...) then skips the unselected rows
+ * below the cursor.  Each element is multiplied once, by the same factor: the
+ * weights come out bit-identical to the update doing all of it. */
+size_t dionw_decay_job_bytes(void);
+int dionw_decay_job_begin(void* job, void* const* weights, const int32_t* const* rowmap,
+                          const int64_t* rows_per_tensor, int n_tensors, int64_t rows,
+                          int64_t cols, float decay_factor, const float* decay_device,
+                          int rows_per_wait, void* stream);
+void dionw_gemm_side_job(void* job);
 
 /* dst[0..n) <- values[0..n) (host array), stream-ordered: the values are copied
  * into the launch, so the host array may be reused at once.  The step's scalars

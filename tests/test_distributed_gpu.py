@@ -198,6 +198,60 @@ def _ema_worker(rank: int, world: int, port: int, failures, ema_device: str) -> 
         dist.destroy_process_group()
 
 
+def _decay_job_worker(rank: int, world: int, port: int, failures) -> None:
+    """Blocks whose products are long enough to carry the round's decay job (K >= 1536): the sharded
+    step with the job equals single-GPU ``Dion`` bit for bit, and the job did take rows."""
+    import torch.distributed as dist
+
+    import dionw_b200 as dionw
+    from dionw_b200 import _workspace
+    from dionw_b200.distributed import ShardedDion
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        def build(cls):
+            torch.manual_seed(3)
+            net = nn.Module()
+            net.tall = nn.ParameterList([nn.Parameter(torch.randn(4096, 2048) * 0.02) for _ in range(3)])
+            net.wide = nn.ParameterList([nn.Parameter(torch.randn(1024, 4096) * 0.02) for _ in range(2)])
+            net.norm = nn.Parameter(torch.randn(256) * 0.02)
+            net = net.to(device)
+            groups, _ = dionw.param_groups(net, fraction=0.25)
+            return net, cls(groups, lr=3e-4, weight_decay=0.05)
+
+        single_net, single = build(dionw.Dion)
+        sharded_net, sharded = build(ShardedDion)
+        assert sharded.fused_decay
+        taken = 0
+        for step in range(3):
+            gen = torch.Generator().manual_seed(200 + step)
+            for a, b in zip(single_net.parameters(), sharded_net.parameters()):
+                g = (torch.randn(a.shape, generator=gen) * 1e-3).to(device)
+                a.grad, b.grad = g.clone(), g.clone()
+            single.step()
+            sharded.step()
+            torch.cuda.synchronize()
+            for a, b in zip(single_net.parameters(), sharded_net.parameters()):
+                assert torch.equal(a, b), f"step {step}: weights differ"
+            for parity in (0, 1):
+                job = _workspace._arenas.get((device, f"decayjob{parity}"))
+                if job is not None:
+                    taken += int(job[20:24].view(torch.int32))
+        assert taken > 0, "no product took a row of a decay job"
+        want, got = single.state_dict(), sharded.state_dict()
+        for index, entry in want["state"].items():
+            for key, value in entry.items():
+                assert torch.equal(value, got["state"][index][key]), (index, key)
+    except Exception as exc:  # reported to the parent
+        import traceback
+        failures.put(f"rank {rank}: {exc!r}\n{traceback.format_exc()}")
+    finally:
+        dist.destroy_process_group()
+
+
 def _run_two_ranks(target, *extra) -> None:
     _run_ranks(2, target, *extra)
 
@@ -219,6 +273,15 @@ def _run_ranks(world: int, target, *extra) -> None:
 @pytest.mark.parametrize("overlap", [False, True])
 def test_sharded_step_equals_single_gpu_step(overlap) -> None:
     _run_two_ranks(_worker, overlap)
+
+
+def test_decay_job_in_a_group_of_one_equals_single_gpu_step() -> None:
+    _run_ranks(1, _decay_job_worker)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_decay_job_on_two_gpus_equals_single_gpu_step() -> None:
+    _run_two_ranks(_decay_job_worker)
 
 
 @pytest.mark.parametrize("overlap", [False, True])

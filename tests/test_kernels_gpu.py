@@ -717,3 +717,69 @@ def test_tiles_drawn_from_a_counter_give_the_same_bits(native) -> None:
         assert rel_l2(got[0], a.float() @ a.float().mT) < 2e-3
     finally:
         native.gemm_dynamic_tiles(was)
+
+
+def test_products_decay_unselected_rows_while_they_wait(native) -> None:
+    """A decay job carried by a long product: its epilogue warps multiply unselected rows of the job's
+    weights by the decay factor while they wait; the update kernel given the same job skips those and
+    does the rest.  The weights equal, bit for bit, the update kernel doing all of it -- whatever
+    share of the rows the product got to (here it must get to some)."""
+    g = _gen(50)
+    rows, cols, k = 512, 1024, 128
+    ld = cols
+    factor = 1.0 - 3e-4 * 0.05
+    blocks_per_tensor = [2, 1, 3]
+    count = sum(blocks_per_tensor)
+    o = (torch.randn(count, k, ld, generator=g) * 0.05).bfloat16().to(DEV)
+    index = oracle.select_rows(torch.rand(count, rows, generator=g), k)
+    rowmap = torch.full((count, rows), -1, dtype=torch.int32)
+    rowmap.scatter_(1, index, torch.arange(k, dtype=torch.int32).expand(count, k))
+    rowmap = rowmap.to(DEV)
+    denom = (torch.rand(count * k, generator=g) + 0.5).to(DEV)
+    scale = (torch.rand(count, generator=g) * -0.01).to(DEV)
+    start = [torch.randn(b * rows, cols, generator=g) * 0.02 for b in blocks_per_tensor]
+    per_tensor = [b * rows for b in blocks_per_tensor]
+
+    def tables(weights):
+        o_p, m_p, d_p, s_p, block = [], [], [], [], 0
+        for b in blocks_per_tensor:
+            o_p.append(o[block].data_ptr()); m_p.append(rowmap[block].data_ptr())
+            d_p.append(denom[block * k:].data_ptr()); s_p.append(scale[block:].data_ptr())
+            block += b
+        return o_p, m_p, d_p, s_p
+
+    expect = [t.to(DEV) for t in start]
+    o_p, m_p, d_p, s_p = tables(expect)
+    native.apply_round(expect, per_tensor, o_p, m_p, d_p, s_p, ldo=ld, rows=rows, k=k, cols=cols,
+                       decay_factor=factor, has_decay=True)
+    got = [t.to(DEV) for t in start]
+    job = torch.zeros(native.decay_job_bytes(), dtype=torch.uint8, device=DEV)
+    native.decay_job_begin(job, got, m_p, per_tensor, rows=rows, cols=cols, decay_factor=factor, rows_per_wait=2)
+    a = (torch.randn(4, 1536, 4096, generator=g) / 64).half().to(DEV)     # K = 4096: a long main loop, 84 tiles
+    out = torch.empty(4, 1536, 1536, dtype=torch.float16, device=DEV)
+    plain = torch.empty_like(out)
+    native.symmetric_product(a, plain)
+    native.gemm_side_job(job)
+    try:
+        native.symmetric_product(a, out)
+    finally:
+        native.gemm_side_job(None)
+    torch.cuda.synchronize()
+    taken = int(job[20:24].view(torch.int32))
+    assert taken > 0, "the product's epilogue warps took no row of the job"
+    assert torch.equal(out, plain)
+    half_done = [t.clone() for t in got]
+    native.apply_round(got, per_tensor, o_p, m_p, d_p, s_p, ldo=ld, rows=rows, k=k, cols=cols,
+                       decay_factor=factor, has_decay=True, decay_job=job)
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    for mine, want in zip(got, expect):
+        assert torch.equal(mine, want)
+    # what the product did: unselected rows below the cursor are decayed exactly once, nothing else is touched
+    flat_map = rowmap.view(-1).cpu()
+    before, after = torch.cat(start), torch.cat([t.cpu() for t in half_done])
+    done = min(taken, before.shape[0])
+    unselected = flat_map[:done] < 0
+    assert torch.equal(after[:done][unselected], before[:done][unselected] * torch.tensor(factor, dtype=torch.float32))
+    assert torch.equal(after[:done][~unselected], before[:done][~unselected])
+    assert torch.equal(after[done:], before[done:])
