@@ -907,7 +907,7 @@ def run_gpu_arm(args) -> None:
     if distributed:
         from dionw_b200.distributed import ShardedDion
 
-        optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema)
+        optimizer = ShardedDion(groups, lr=LR, weight_decay=WEIGHT_DECAY, ema=ema, fused_decay=args.fused_decay)
         if args.no_overlap:
             optimizer.overlap_apply = False
         if args.overlap_apply:
@@ -922,8 +922,6 @@ def run_gpu_arm(args) -> None:
             optimizer.costliest_second = False
         if args.static_tiles:
             _native.gemm_dynamic_tiles(False)
-        if args.no_fused_decay:
-            optimizer.fused_decay = False
         if args.decay_rows_per_wait >= 0:
             optimizer.decay_rows_per_wait = args.decay_rows_per_wait
         if args.adamw_delay_rounds >= 0:
@@ -1236,8 +1234,8 @@ def main() -> None:
     parser.add_argument("--round-elements", type=int, default=0, help="sharded step: update elements per round")
     parser.add_argument("--max-run-elements", type=int, default=0,
                         help="update elements one run orthogonalizes at once (default: the reference's 2^28)")
-    parser.add_argument("--no-fused-decay", action="store_true",
-                        help="sharded step: the weight update kernel decays every row itself (for comparison)")
+    parser.add_argument("--fused-decay", action="store_true",
+                        help="sharded step: the tensor-core products' waiting epilogue warps decay the unselected rows")
     parser.add_argument("--decay-rows-per-wait", type=int, default=-1,
                         help="sharded step: rows of the decay job an epilogue warp may take per tile it waits for")
     parser.add_argument("--static-tiles", action="store_true",

@@ -161,7 +161,8 @@ class _ShardedCore(_DionCore):
 
     def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
                  muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.0,
-                 eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE, process_group: Any = None) -> None:
+                 eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE, process_group: Any = None,
+                 fused_decay: bool = False) -> None:
         import torch.distributed as dist
 
         if not dist.is_initialized():
@@ -170,6 +171,7 @@ class _ShardedCore(_DionCore):
         self._pg = process_group
         self._world = dist.get_world_size(process_group)
         self._rank = dist.get_rank(process_group)
+        self.fused_decay = bool(fused_decay)
         # The rounds' row maps travel on a communicator of their own: NCCL runs the collectives of one
         # communicator in the order they were issued, and a 60 KB exchange that the round's products
         # wait for must not queue behind the previous round's results or AdamW's ranges (2 GPUs,
@@ -433,12 +435,15 @@ class _ShardedCore(_DionCore):
 
     # The decoupled decay of the rows a round does NOT select (three quarters of the 8 B per weight
     # element that every rank spends on the update) depends on nothing but the row maps, which exist
-    # after `select`, before the round's first product.  With ``fused_decay`` the ranks exchange
-    # their row maps right there (a small all-gather), describe the round's weights in a decay job
-    # (csrc/decay_job.cuh), and the round's tensor-core products carry it: their epilogue warps decay
-    # rows while they wait for their accumulators.  The update kernel then skips what the job's
-    # cursor covers.  Same multiplication, once per element: bit-identical weights.
-    fused_decay = True
+    # after `select`, before the round's first product.  With ``fused_decay=True`` (constructor
+    # argument; off by default) the ranks exchange their row maps right there (a small all-gather on
+    # a communicator of its own), describe the round's weights in a decay job (csrc/decay_job.cuh),
+    # and the round's tensor-core products carry it: their epilogue warps decay rows while they wait
+    # for their accumulators.  The update kernel then skips what the job's cursor covers.  Same
+    # multiplication, once per element: bit-identical weights.  Measured (Llama-3-8B shapes, ms,
+    # off -> on): 2 GPUs update 10.7 -> 7.7, Newton-Schulz 32.8 -> 34.6, step 56.8 -> 56.5; 4 GPUs update
+    # 10.6 -> 7.5, Newton-Schulz 17.6 -> 19.8, step 35.4 -> 34.9: the products are bound by what the L2
+    # delivers to the SMs, so rows streamed beside them cost them nearly what they save the update.
     decay_rows_per_wait = 2
 
     def _begin_decay_job(self, sb: _SharedBucket, group: dict[str, Any], chosen: list[list[int]], counts: list[int],
@@ -630,10 +635,11 @@ class ShardedDion(IntegratedEMAOptimizer, _ShardedCore):
     def __init__(self, params: Iterable[dict[str, Any]], *, lr: float, momentum: float = 0.95,
                  muon_beta2: float = 0.95, betas: tuple[float, float] = (0.9, 0.95), weight_decay: float = 0.0,
                  eps: float = 1e-8, matrix_update: MatrixUpdate = DION3_UPDATE, process_group: Any = None,
-                 ema: EMAConfig | None = None, profile_region: ProfileRegion = no_profile) -> None:
+                 ema: EMAConfig | None = None, profile_region: ProfileRegion = no_profile,
+                 fused_decay: bool = False) -> None:
         super().__init__(params, lr=lr, momentum=momentum, muon_beta2=muon_beta2, betas=betas,
                          weight_decay=weight_decay, eps=eps, matrix_update=matrix_update,
-                         process_group=process_group)
+                         process_group=process_group, fused_decay=fused_decay)
         self._init_integrated_ema(ema, profile_region)
         if self._ema_helper is not None:
             self._ema_helper.source_view = self._ema_view

@@ -212,7 +212,7 @@ def _decay_job_worker(rank: int, world: int, port: int, failures) -> None:
     device = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
-        def build(cls):
+        def build(cls, **kw):
             torch.manual_seed(3)
             net = nn.Module()
             net.tall = nn.ParameterList([nn.Parameter(torch.randn(4096, 2048) * 0.02) for _ in range(3)])
@@ -220,10 +220,10 @@ def _decay_job_worker(rank: int, world: int, port: int, failures) -> None:
             net.norm = nn.Parameter(torch.randn(256) * 0.02)
             net = net.to(device)
             groups, _ = dionw.param_groups(net, fraction=0.25)
-            return net, cls(groups, lr=3e-4, weight_decay=0.05)
+            return net, cls(groups, lr=3e-4, weight_decay=0.05, **kw)
 
         single_net, single = build(dionw.Dion)
-        sharded_net, sharded = build(ShardedDion)
+        sharded_net, sharded = build(ShardedDion, fused_decay=True)
         assert sharded.fused_decay
         taken = 0
         for step in range(3):
