@@ -442,8 +442,8 @@ class _ShardedCore(_DionCore):
     # for their accumulators.  The update kernel then skips what the job's cursor covers.  Same
     # multiplication, once per element: bit-identical weights.  Measured (Llama-3-8B shapes, ms,
     # off -> on): 2 GPUs update 10.7 -> 7.7, Newton-Schulz 32.8 -> 34.6, step 56.8 -> 56.5; 4 GPUs update
-    # 10.6 -> 7.5, Newton-Schulz 17.6 -> 19.8, step 35.4 -> 34.9: the products are bound by what the L2
-    # delivers to the SMs, so rows streamed beside them cost them nearly what they save the update.
+    # 10.6 -> 7.5, Newton-Schulz 17.6 -> 19.8, step 35.4 -> 34.9: during the products the board is at its
+    # power cap, so the joules of the rows streamed beside them come out of the products' clock.
     decay_rows_per_wait = 2
 
     def _begin_decay_job(self, sb: _SharedBucket, group: dict[str, Any], chosen: list[list[int]], counts: list[int],
