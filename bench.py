@@ -883,7 +883,7 @@ def run_gpu_arm(args) -> None:
     reference_gpu = None
     if world == 1 and not args.sharded and not args.no_reference_gpu and not args.graph_replay and args.ema == "config":
         reference_gpu = run_sub_bench(["--impl", "reference-gpu", "--config", args.config, "--steps",
-                                       str(min(10, args.steps)), "--warmup", "3"], timeout=600)
+                                       str(min(10, args.steps)), "--warmup", "3"], timeout=300)
         reference_gpu = {k: reference_gpu.get(k) for k in ("value", "median_ms", "unit", "steps", "warmup", "clocks",
                                                            "config", "unavailable") if k in reference_gpu}
     parity = sharded_parity(device, rank, dist) if distributed and not args.no_parity else None
@@ -1147,7 +1147,7 @@ def run_gpu_arm(args) -> None:
         pool.clear()
         _workspace.release()
         torch.cuda.empty_cache()
-        sub = run_sub_bench(["--config", "gram-ns", "--steps", "5", "--warmup", "3"], timeout=600)
+        sub = run_sub_bench(["--config", "gram-ns", "--steps", "5", "--warmup", "3"], timeout=240)
         gram_ns = sub if "unavailable" in sub else {
             "shapes": [{k: row[k] for k in ("shape", "batch", "iteration_ms", "call_ms", "TFLOP/s", "executed_TFLOP/s",
                                             "frac_of_burst_peak", "executed_frac_of_burst_peak", "orthogonality_error")
