@@ -3,8 +3,10 @@
  *
  * Every entry point takes raw device pointers, sizes and the CUDA stream to
  * launch on (passed as void* so that this header needs no CUDA include), runs
- * asynchronously on that stream, allocates nothing, never synchronises, and
- * returns DIONW_OK or a negative code; dionw_last_error() then gives the text.
+ * asynchronously on that stream, allocates nothing, never synchronises (the two
+ * status reads, dionw_device_status and dionw_check_device, and the CPU EMA
+ * job's waits excepted), and returns DIONW_OK or a negative code;
+ * dionw_last_error() then gives the text.
  * The reference has no FFI of its own: each entry replaces the Python/Triton
  * function cited beside it (paths are relative to the reference project).
  *
