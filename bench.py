@@ -1147,12 +1147,18 @@ def run_gpu_arm(args) -> None:
         pool.clear()
         _workspace.release()
         torch.cuda.empty_cache()
-        sub = run_sub_bench(["--config", "gram-ns", "--steps", "5", "--warmup", "3"], timeout=240)
+        sub = run_sub_bench(["--config", "gram-ns", "--steps", "3", "--warmup", "3"], timeout=240)
         gram_ns = sub if "unavailable" in sub else {
             "shapes": [{k: row[k] for k in ("shape", "batch", "iteration_ms", "call_ms", "TFLOP/s", "executed_TFLOP/s",
                                             "frac_of_burst_peak", "executed_frac_of_burst_peak", "orthogonality_error")
                         if k in row} for row in sub.get("shapes", [])],
             "clocks": sub.get("clocks"), "steps": sub.get("steps"), "warmup": sub.get("warmup")}
+        # the reference's own Gram Newton-Schulz entry on the same batches (whole call; its Triton + cuBLAS products)
+        theirs = run_sub_bench(["--impl", "reference-gpu", "--config", "gram-ns", "--steps", "3", "--warmup", "3"],
+                               timeout=240)
+        gram_ns["reference"] = theirs if "unavailable" in theirs else [
+            {k: row[k] for k in ("shape", "call_ms", "TFLOP/s_of_call", "orthogonality_error") if k in row}
+            for row in theirs.get("shapes", [])]
     line = {
         "metric": "optimizer_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
