@@ -119,6 +119,24 @@ def _require_same_structure(saved: list[dict[str, Any]], current: list[dict[str,
                     "Build the groups as the checkpoint was built to resume it.")
 
 
+def step_scalar_values(groups: list[dict[str, Any]], owners: list[Any]) -> tuple[list[float], int]:
+    """The step's scalars in table order, and the index of the first per-bucket slot.
+
+    Four slots per group -- lr, weight decay, ``1 - lr * weight_decay`` (computed in Python doubles and
+    rounded once when the table is written, as src/dionw/_matrix_step.py:280 computes it), one unused --
+    then one slot per owner: ``-step_size`` for a ``Bucket`` (src/dionw/_matrix_step.py:115, :147-159),
+    0 for anything else (a sharded optimizer lists buckets owned elsewhere, which need only their
+    group's decay factor)."""
+    values: list[float] = []
+    for group in groups:
+        lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
+        values += [lr, weight_decay, 1.0 - lr * weight_decay, 0.0]
+    base = len(values)
+    for owner in owners:
+        values.append(-step_size(owner, float(groups[owner.group_index]["lr"])) if isinstance(owner, Bucket) else 0.0)
+    return values, base
+
+
 class _DionCore(Optimizer):
     """The matrix and AdamW updates over routed param groups (no EMA)."""
 
@@ -261,13 +279,7 @@ class _DionCore(Optimizer):
 
         owners = self._scalar_slots()
         groups = self.param_groups
-        values: list[float] = []
-        for group in groups:
-            lr, weight_decay = float(group["lr"]), float(group["weight_decay"])
-            values += [lr, weight_decay, 1.0 - lr * weight_decay, 0.0]
-        base = len(values)
-        for owner in owners:
-            values.append(-step_size(owner, float(groups[owner.group_index]["lr"])) if isinstance(owner, Bucket) else 0.0)
+        values, base = step_scalar_values(groups, owners)
         layout = (len(groups), sum(len(group["params"]) for group in groups), tuple(id(o) for o in owners))
         if layout != self._scalar_layout:
             devices = sorted({p.device for group in groups for p in group["params"] if p.is_cuda},

@@ -195,3 +195,30 @@ def test_snapshot_chunks_keep_order_and_balance() -> None:
     assert all(chunk for chunk in chunks)
     one = [(0, torch.empty(1 << 26, device="meta"))]
     assert tracker._snapshot_chunks(one) == [one]
+
+
+def test_step_scalar_table_layout_and_values() -> None:
+    """The device table of step scalars: four slots per group, then ``-step_size`` per bucket, with the
+    reference's formulas (src/dionw/_matrix_step.py:147-159 for the step size, :280 for the decay)."""
+    import math
+
+    from dionw_b200._buckets import Bucket
+    from dionw_b200.optimizer import step_scalar_values
+
+    groups = [{"lr": 3e-4, "weight_decay": 0.0}, {"lr": 1e-3, "weight_decay": 0.05}]
+    empty = torch.zeros(0)
+    selecting = Bucket(group_index=1, orthogonalize=None, params=[], slices=[], rows=14336, cols=4096,
+                       selected_rows=3584, momentum=empty, variance=empty)
+    full = Bucket(group_index=1, orthogonalize=None, params=[], slices=[], rows=768, cols=2304,
+                  selected_rows=768, momentum=empty, variance=empty)
+
+    class Elsewhere:   # a bucket another rank owns: only its group's decay factor matters
+        group_index = 1
+
+    values, base = step_scalar_values(groups, [selecting, Elsewhere(), full])
+    assert base == 8 and len(values) == 11
+    assert values[:4] == [3e-4, 0.0, 1.0, 0.0]
+    assert values[4:8] == [1e-3, 0.05, 1.0 - 1e-3 * 0.05, 0.0]
+    assert values[8] == -(1e-3 * 0.2 * math.sqrt(14336) * math.sqrt(4096 / 3584))
+    assert values[9] == 0.0
+    assert values[10] == -(1e-3 * 0.2 * math.sqrt(2304) * math.sqrt(768 / 768))
