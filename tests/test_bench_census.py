@@ -60,3 +60,25 @@ def test_cpu_arm_runs_the_single_matrix_workload_whole() -> None:
     assert 0.0 < base["sample_ms"] <= base["value"] * 1.0001
     assert base["value"] == pytest.approx(base["sample_ms"], rel=1e-6)   # scale factors are 1
     assert "whole workload" in base["sample"]
+
+
+def test_per_operand_newton_schulz_rows_are_split_out_of_the_stages() -> None:
+    """``ns:<m>x<n>`` entries leave the stage dictionary (so that the stage sum still is the step) and
+    come back as rows with executed and algorithmic rates."""
+    stages = {"accumulate": 14.6, "newton_schulz": 59.2, "ns:3584x4096": 51.0, "ns:256x4096": 0.55}
+    blocks = {"ns:3584x4096": 64 * 10, "ns:256x4096": 64 * 10}
+    rows = bench.split_ns_shapes(stages, blocks, steps=10)
+    assert set(stages) == {"accumulate", "newton_schulz"} and not blocks
+    by_operand = {tuple(r["operand"]): r for r in rows}
+    big = by_operand[(3584, 4096)]
+    assert big["blocks"] == 64 and big["ms"] == 51.0
+    assert big["executed_TFLOP/s"] == pytest.approx(64 * bench.flops_newton_schulz_executed(3584, 4096) / 51.0 / 1e9)
+    assert big["algorithmic_TFLOP/s"] == pytest.approx(64 * bench.flops_newton_schulz(3584, 4096) / 51.0 / 1e9)
+    assert big["executed_TFLOP/s"] < big["algorithmic_TFLOP/s"]
+
+
+def test_a_sub_benchmark_that_prints_no_line_is_reported_not_raised() -> None:
+    """The embedded arms (the reference's GPU step, the microbenchmark) run in processes of their own; one
+    that fails leaves an ``unavailable`` entry with the reason instead of stopping the run."""
+    result = bench.run_sub_bench(["--config", "no-such-config"], timeout=120)
+    assert "unavailable" in result and "no JSON line" in result["unavailable"]
