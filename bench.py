@@ -875,7 +875,10 @@ def run_gpu_arm(args) -> None:
             for key, value in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533"), ("RANK", "0"),
                                ("WORLD_SIZE", "1")):
                 os.environ.setdefault(key, value)
-        dist.init_process_group("nccl", device_id=device)
+        options = None
+        if args.nccl_high_priority:   # NCCL's kernels on a high-priority stream (an experiment switch)
+            options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=device, pg_options=options)
     _native.library()
     # The reference's own GPU step on the same workload (its Triton + cuBLAS path), measured first, in a
     # process of its own, while this one holds no device memory: the denominator of "times faster than
@@ -1226,6 +1229,8 @@ def main() -> None:
                         help="one GPU: do not time the reference's own GPU step and the Newton-Schulz microbenchmark "
                              "in processes of their own before and after this arm")
     parser.add_argument("--no-overlap", action="store_true", help="one-stream step (for comparison)")
+    parser.add_argument("--nccl-high-priority", action="store_true",
+                        help="create the process group with NCCL's kernels on a high-priority stream")
     parser.add_argument("--adamw-delay-rounds", type=int, default=-1,
                         help="sharded step: rounds between the costliest bucket's last round and AdamW (default 1)")
     parser.add_argument("--adamw-late", action="store_true",
